@@ -35,6 +35,7 @@ class PagedCacheSpec:
     key_dim: int
     value_dim: int = 0
     window: int = 0        # 0: every position is kept; n: only the last n positions are ever read
+    chunk: int = 0         # n > 0: a query at position p reads only positions >= (p // n) * n
 
     def __post_init__(self) -> None:
         if self.value_dim == 0:
@@ -50,7 +51,7 @@ class PagedCacheSpec:
 
     @property
     def group_key(self) -> tuple:
-        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window)
+        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window, self.chunk)
 
 
 @dataclass(frozen=True)
@@ -135,6 +136,7 @@ class GroupState:
     window: int
     cache_ids: list[int]
     pool: PagePool
+    chunk: int = 0
 
 
 @dataclass
@@ -170,11 +172,11 @@ class CacheManager:
         by_key: dict[tuple, int] = {}
         for cache_id, spec in enumerate(self.cache_specs):
             if isinstance(spec, PagedCacheSpec):
-                if spec.window < 0:
-                    raise InvalidArgumentError("a window cannot be negative")
+                if spec.window < 0 or spec.chunk < 0:
+                    raise InvalidArgumentError("a window or chunk cannot be negative")
                 if spec.group_key not in by_key:
                     by_key[spec.group_key] = len(self.groups)
-                    self.groups.append(GroupState(spec.group_key, spec.window, [], PagePool(num_pages)))
+                    self.groups.append(GroupState(spec.group_key, spec.window, [], PagePool(num_pages), spec.chunk))
                 index = by_key[spec.group_key]
                 self.groups[index].cache_ids.append(cache_id)
                 self.group_of_cache[cache_id] = index
@@ -197,9 +199,10 @@ class CacheManager:
         """Pages a request of ``length`` positions holds at most at one time in ``group``, when no step
         brings more than ``step_tokens`` new positions."""
         full = self.blocks_for(length)
-        if group.window == 0:
+        reach = min([n for n in (group.window, group.chunk) if n > 0], default=0)
+        if reach == 0:
             return full
-        return min(full, self.blocks_for(group.window + step_tokens) + 1)
+        return min(full, self.blocks_for(reach + step_tokens) + 1)
 
     def num_free_pages(self, group: int = 0) -> int:
         return self.groups[group].pool.num_free
@@ -281,15 +284,21 @@ class CacheManager:
     def commit(self, request_id: Hashable, computed: int) -> None:
         """Record that positions [0, computed) are written, and give back the pages of windowed
         groups that no later query can see: a query at position p >= computed reads keys
-        > p - window, so block b is dead once (b + 1) * page_size <= computed - window + 1."""
+        > p - window, so block b is dead once (b + 1) * page_size <= computed - window + 1; in a
+        chunked group it reads keys >= (p // chunk) * chunk, so block b is dead once
+        (b + 1) * page_size <= (computed // chunk) * chunk."""
         request = self._requests[request_id]
         if computed > request.length:
             raise InvalidArgumentError("cannot commit positions the tables do not cover")
         request.computed = max(request.computed, computed)
         for index, group in enumerate(self.groups):
-            if group.window == 0:
+            if group.window == 0 and group.chunk == 0:
                 continue
-            dead = max(0, (request.computed - group.window + 1) // self.page_size)
+            dead = 0
+            if group.window > 0:
+                dead = max(dead, (request.computed - group.window + 1) // self.page_size)
+            if group.chunk > 0:
+                dead = max(dead, (request.computed // group.chunk) * group.chunk // self.page_size)
             dead = min(dead, len(request.tables[index]))
             if dead > request.released_blocks[index]:
                 table = request.tables[index]
@@ -329,7 +338,8 @@ class CacheManager:
                 assert len(table) == self.blocks_for(request.length), "table length does not match the positions"
                 for block, page in enumerate(table):
                     if page == NULL_PAGE:
-                        assert group.window > 0 and block < request.released_blocks[index], "hole in a table"
+                        assert (group.window > 0 or group.chunk > 0) and block < request.released_blocks[index], \
+                            "hole in a table"
                         continue
                     assert 0 < page < group.pool.num_pages, f"page {page} out of range"
                     assert page not in held, f"page {page} held by {held[page]!r} and {request_id!r}"

@@ -78,6 +78,21 @@ class CacheStorage:
         for cache_id in manager.state_cache_ids:
             self.tensors[cache_id][slot].zero_()
 
+    def snapshot_state(self, manager: CacheManager, slots: list[int]):
+        """Copies of the given slots of every state cache (None if the model keeps no state): a step that
+        is run twice (once to warm up before its capture, once for real) puts them back in between."""
+        if not manager.state_cache_ids:
+            return None
+        index = torch.tensor(list(slots), dtype=torch.long, device=self.tensors[manager.state_cache_ids[0]].device)
+        return index, [self.tensors[cache_id].index_select(0, index) for cache_id in manager.state_cache_ids]
+
+    def restore_state(self, manager: CacheManager, snapshot) -> None:
+        if snapshot is None:
+            return
+        index, saved = snapshot
+        for cache_id, values in zip(manager.state_cache_ids, saved):
+            self.tensors[cache_id].index_copy_(0, index, values)
+
     def poison_pages(self, manager: CacheManager, group: int, pages: list[int]) -> None:
         """Fill given-back pages with NaN (tests: a kernel that reads a page it should not shows up)."""
         live = [p for p in pages if p != 0]

@@ -16,6 +16,7 @@ from pathlib import Path
 from typing import Any, Mapping
 
 from .errors import ConfigError
+from .legelix import LegelixConfig
 from .qwen3 import Qwen3Config
 from .spec import ModelSpec
 
@@ -54,6 +55,8 @@ def resolve_architecture(config: Mapping[str, Any], where: str = "config.json") 
     has_model_type = "model_type" in config
     model_type = config.get("model_type", "")
     architectures = config.get("architectures") or []
+    if not architectures and isinstance(config.get("architecture"), str):
+        architectures = [config["architecture"]]       # some designs name themselves under a single key
     if not isinstance(architectures, list) or any(not isinstance(a, str) for a in architectures):
         raise ConfigError(f"{where}: 'architectures' must be a list of strings")
     if len(architectures) > 1:
@@ -103,3 +106,4 @@ def load_model_spec(model_dir: str | Path) -> ModelSpec:
 
 
 register_architecture(Qwen3Config.model_type, Qwen3Config.architecture, Qwen3Config)
+register_architecture(LegelixConfig.model_type, LegelixConfig.architecture, LegelixConfig)

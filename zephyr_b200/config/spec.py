@@ -24,6 +24,7 @@ class NormSpec:
     size: int
     eps: float
     weight: str        # full tensor name of the scale
+    bias: str | None = None    # full tensor name of the shift, for norms that have one
 
 
 @dataclass(frozen=True)
@@ -65,8 +66,9 @@ class LayerSpec:
 
     block: str         # key in parts.BLOCKS, e.g. "prenorm_residual"
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: FeedForwardSpec | None      # None: a layer without a feed-forward (where the block allows it)
     norms: Mapping[str, NormSpec]
+    block_params: Mapping[str, Any] = field(default_factory=dict)   # the arrangement's own constants
 
 
 @dataclass(frozen=True)
@@ -93,12 +95,20 @@ class LayerCall:
     weights run again).  ``cache`` names the cache this call's mixer uses;
     calls with equal ``cache`` share it.  Only a call with ``writes_cache``
     stores new entries; a call without it reads what an earlier call of the
-    same step stored (a layer that reads another layer's cache).
+    same step stored (a layer that reads another layer's cache).  A mixer that
+    keeps several stores (its ``cache_spec`` returns a tuple: pages beside a
+    fixed state, or the stores of mixers that run side by side) gets the first
+    under ``cache`` and the others under ``extra_caches``, in that order.
     """
 
     layer: int
     cache: int
     writes_cache: bool = True
+    extra_caches: tuple[int, ...] = ()
+
+    @property
+    def caches(self) -> tuple[int, ...]:
+        return (self.cache, *self.extra_caches)
 
 
 @dataclass(frozen=True)
@@ -116,7 +126,7 @@ class ModelSpec:
 
     @property
     def num_caches(self) -> int:
-        return 1 + max(call.cache for call in self.run_order)
+        return 1 + max(cache for call in self.run_order for cache in call.caches)
 
     def validate(self) -> None:
         from .errors import ConfigError
@@ -127,14 +137,15 @@ class ModelSpec:
         for index, call in enumerate(self.run_order):
             if not 0 <= call.layer < len(self.layers):
                 raise ConfigError(f"run_order[{index}] names layer {call.layer}, which does not exist")
-            if call.cache < 0:
-                raise ConfigError(f"run_order[{index}] has a negative cache id")
-            if call.writes_cache:
-                if call.cache in writers:
-                    raise ConfigError(
-                        f"cache {call.cache} is written by run_order[{writers[call.cache]}] and run_order[{index}]")
-                writers[call.cache] = index
-            elif call.cache not in writers:
-                raise ConfigError(f"run_order[{index}] reads cache {call.cache} before any call has written it")
+            for cache in call.caches:
+                if cache < 0:
+                    raise ConfigError(f"run_order[{index}] has a negative cache id")
+                if call.writes_cache:
+                    if cache in writers:
+                        raise ConfigError(
+                            f"cache {cache} is written by run_order[{writers[cache]}] and run_order[{index}]")
+                    writers[cache] = index
+                elif cache not in writers:
+                    raise ConfigError(f"run_order[{index}] reads cache {cache} before any call has written it")
         if sorted(writers) != list(range(self.num_caches)):
             raise ConfigError("cache ids must be 0..n-1, each written by exactly one call")

@@ -11,6 +11,12 @@
 // in the distance (a slope per query head), is added here; the one architecture has none, and
 // the faster kernels do not take one.
 //
+// Keys and values may differ in width (kd, vd): a page holds its keys [nkv][page_size][kd] and behind
+// them its values [nkv][page_size][vd].  Two more masks and one more term of the softmax are taken as
+// parameters: `chunk` > 0 lets a query at position p see only keys j with j / chunk == p / chunk
+// (chunks counted from position 0 of the sequence); `sinks` (one float32 per query head) adds
+// exp(sink) to the softmax's denominator, a term without key or value that is not scaled.
+//
 // One CTA serves one tile: a run of consecutive new tokens of one request, one key/value head,
 // and a chunk of that head's query heads.  The (token, head) pairs of the tile are dealt to the
 // warps; key/value tiles of 32 positions are staged in shared memory once and used by all pairs.
@@ -24,9 +30,9 @@ constexpr int ATT_MAX_PAIRS = ATT_WARPS * ATT_PAIRS_PER_WARP;   // 16 (token, he
 constexpr int ATT_TILE = 32;                                    // keys per shared-memory tile
 
 struct AttentionArgs {
-  const void* q;            // [T, nh*hd]
-  void* out;                // [T, nh*hd]
-  const void* kv_cache;     // [num_pages][2][nkv][page_size][hd]
+  const void* q;            // [T, nh*kd]
+  void* out;                // [T, nh*vd]
+  const void* kv_cache;     // [num_pages]{[nkv][page_size][kd], [nkv][page_size][vd]}
   const int* block_table;   // [R, max_blocks]
   const int* tile_row;      // [n_tiles] request row of the tile
   const int* tile_q0;       // [n_tiles] offset of the tile's first token within the row's new tokens
@@ -34,8 +40,9 @@ struct AttentionArgs {
   const int* row_q_len;     // [R]
   const int* row_ctx;       // [R] tokens already in the cache before this step
   int max_blocks, page_size, num_pages, num_rows;
-  int nh, nkv, hd, window, tile_tokens, heads_per_chunk;
+  int nh, nkv, kd, vd, window, chunk, tile_tokens, heads_per_chunk;
   float scale;
+  const float* sinks;        // null, or [nh]: exp(sinks[h]) joins the denominator of head h's softmax
   const float* head_slopes;  // null, or [nh]: query head h adds head_slopes[h] * (key position - query position) to its scores
   int* status;
 };
@@ -44,15 +51,54 @@ template <typename T> struct KPad;
 template <> struct KPad<float> { static constexpr int N = 1; };
 template <> struct KPad<__nv_bfloat16> { static constexpr int N = 2; };
 
+// Rows k0 .. k0 + ATT_TILE - 1 of one key/value head (keys or values: `part` is where that half
+// begins inside a page, `dim` its width) into shared memory, un-permuted; zeros outside [lo, hi).
+// Rows whose bytes are a multiple of 16 are stored with permuted 16-byte chunks (common.cuh:
+// kv_swizzle) and move as vectors; any other width is stored as it is and moves element by element.
+template <typename T>
+__device__ __forceinline__ void stage_rows(T* dst, int dst_stride, const T* cache, const AttentionArgs& a, int row,
+                                           int kvh, int k0, int lo, int hi, int dim, long long page_elems,
+                                           long long part, int tok0) {
+  constexpr int vec = 16 / static_cast<int>(sizeof(T));
+  const bool vectors = dim % vec == 0;
+  const int per_row = vectors ? dim / vec : dim;
+  for (int e = threadIdx.x; e < ATT_TILE * per_row; e += blockDim.x) {
+    const int j = e / per_row, c = e - j * per_row;
+    const int pos = k0 + j;
+    bool ok = pos >= lo && pos < hi;
+    long long base = 0;
+    if (ok) {
+      const int block = pos / a.page_size;
+      const int page = block < a.max_blocks ? a.block_table[static_cast<size_t>(row) * a.max_blocks + block] : -1;
+      if (page <= 0 || page >= a.num_pages) {
+        report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
+        ok = false;
+      } else {
+        base = static_cast<long long>(page) * page_elems + part +
+               (static_cast<long long>(kvh) * a.page_size + pos % a.page_size) * dim;
+      }
+    }
+    if (vectors) {
+      uint4 r = make_uint4(0, 0, 0, 0);
+      if (ok) r = *reinterpret_cast<const uint4*>(cache + base + ((c ^ kv_swizzle(pos, per_row)) * vec));
+      const T* re = reinterpret_cast<const T*>(&r);
+#pragma unroll
+      for (int u = 0; u < vec; ++u) dst[j * dst_stride + c * vec + u] = re[u];
+    } else {
+      dst[j * dst_stride + c] = ok ? cache[base + c] : from_float<T>(0.0f);
+    }
+  }
+}
+
 template <typename T, int ACC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_simt_kernel(const AttentionArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int hd = a.hd, g = a.nh / a.nkv;
-  const int kstride = hd + KPad<T>::N;
-  float* q_s = reinterpret_cast<float*>(smem_raw);                       // [ATT_MAX_PAIRS][hd]
-  T* k_s = reinterpret_cast<T*>(q_s + ATT_MAX_PAIRS * hd);               // [ATT_TILE][kstride]
-  T* v_s = k_s + ATT_TILE * kstride;                                      // [ATT_TILE][hd]
+  const int kd = a.kd, vd = a.vd, g = a.nh / a.nkv;
+  const int kstride = kd + KPad<T>::N;
+  float* q_s = reinterpret_cast<float*>(smem_raw);                       // [ATT_MAX_PAIRS][kd]
+  T* k_s = reinterpret_cast<T*>(q_s + ATT_MAX_PAIRS * kd);               // [ATT_TILE][kstride]
+  T* v_s = k_s + ATT_TILE * kstride;                                      // [ATT_TILE][vd]
 
   const int tile = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
@@ -70,11 +116,11 @@ paged_attention_simt_kernel(const AttentionArgs a) {
   const T* cache = static_cast<const T*>(a.kv_cache);
 
   // Queries of all pairs, as float32.
-  for (int e = threadIdx.x; e < n_pairs * hd; e += blockDim.x) {
-    const int p = e / hd, d = e - p * hd;
+  for (int e = threadIdx.x; e < n_pairs * kd; e += blockDim.x) {
+    const int p = e / kd, d = e - p * kd;
     const int qi = p / n_heads, hj = p - qi * n_heads;
     const int head = kvh * g + chunk * a.heads_per_chunk + hj;
-    q_s[p * hd + d] = to_float(q[(static_cast<size_t>(tok0 + qi) * a.nh + head) * hd + d]);
+    q_s[p * kd + d] = to_float(q[(static_cast<size_t>(tok0 + qi) * a.nh + head) * kd + d]);
   }
 
   float m[ATT_PAIRS_PER_WARP], l[ATT_PAIRS_PER_WARP], acc[ATT_PAIRS_PER_WARP][ACC];
@@ -88,44 +134,17 @@ paged_attention_simt_kernel(const AttentionArgs a) {
 
   // Keys any pair of this tile may see: [lo, hi).
   const int hi = ctx + q0 + n_tok;
-  const int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
-  const int vec = 16 / static_cast<int>(sizeof(T));
-  const int chunks_per_row = hd / vec;
+  int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, (ctx + q0) / a.chunk * a.chunk);
+  const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (kd + vd);
+  const long long value_part = static_cast<long long>(a.nkv) * a.page_size * kd;
 
   for (int k0 = lo / ATT_TILE * ATT_TILE; k0 < hi; k0 += ATT_TILE) {
     __syncthreads();     // the previous tile is no longer read (and q_s is complete on the first pass)
-    for (int e = threadIdx.x; e < ATT_TILE * chunks_per_row; e += blockDim.x) {
-      const int j = e / chunks_per_row, d = (e - j * chunks_per_row) * vec;
-      const int pos = k0 + j;
-      bool ok = pos >= lo && pos < hi;
-      long long base = 0;
-      if (ok) {
-        const int block = pos / a.page_size;
-        const int page = block < a.max_blocks ? a.block_table[static_cast<size_t>(row) * a.max_blocks + block] : -1;
-        if (page <= 0 || page >= a.num_pages) {
-          report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, tok0);
-          ok = false;
-        } else {
-          // logical chunk d / vec of the row sits at the permuted chunk (common.cuh: kv_swizzle)
-          base = ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * hd +
-                 (((d / vec) ^ kv_swizzle(pos, chunks_per_row)) * vec);
-        }
-      }
-      // Positions outside [lo, hi) hold zeros: a page that was given back, or one that another
-      // request used before, is never read.
-      uint4 kr = make_uint4(0, 0, 0, 0), vr = make_uint4(0, 0, 0, 0);
-      if (ok) {
-        kr = *reinterpret_cast<const uint4*>(cache + base);
-        vr = *reinterpret_cast<const uint4*>(cache + base + static_cast<long long>(a.nkv) * a.page_size * hd);
-      }
-      const T* ke = reinterpret_cast<const T*>(&kr);
-      const T* ve = reinterpret_cast<const T*>(&vr);
-#pragma unroll
-      for (int u = 0; u < 16 / static_cast<int>(sizeof(T)); ++u) {
-        k_s[j * kstride + d + u] = ke[u];
-        v_s[j * hd + d + u] = ve[u];
-      }
-    }
+    // Positions outside [lo, hi) hold zeros: a page that was given back, or one that another
+    // request used before, is never read.
+    stage_rows<T>(k_s, kstride, cache, a, row, kvh, k0, lo, hi, kd, page_elems, 0, tok0);
+    stage_rows<T>(v_s, vd, cache, a, row, kvh, k0, lo, hi, vd, page_elems, value_part, tok0);
     __syncthreads();
 
     const int kp = k0 + lane;
@@ -136,13 +155,14 @@ paged_attention_simt_kernel(const AttentionArgs a) {
       const int qpos = ctx + q0 + p / n_heads;
       const float slope = a.head_slopes != nullptr
                               ? a.head_slopes[kvh * g + chunk * a.heads_per_chunk + (p - p / n_heads * n_heads)] : 0.0f;
-      const int first = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+      int first = a.window > 0 ? max(0, qpos - a.window + 1) : 0;
+      if (a.chunk > 0) first = max(first, qpos / a.chunk * a.chunk);
       if (k0 > qpos || k0 + ATT_TILE <= first) continue;  // no key of this tile is visible
       const bool valid = kp <= qpos && kp >= first;
       float s = 0.0f;
-      const float* qp = q_s + p * hd;
+      const float* qp = q_s + p * kd;
       const T* kr = k_s + lane * kstride;
-      for (int d = 0; d < hd; d += 2) {
+      for (int d = 0; d < kd; d += 2) {
         s = fmaf(qp[d], to_float(kr[d]), s);
         s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
       }
@@ -160,7 +180,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
 #pragma unroll
         for (int c = 0; c < ACC; ++c) {
           const int d = lane + 32 * c;
-          if (d < hd) acc[i][c] = fmaf(pj, to_float(v_s[j * hd + d]), acc[i][c]);
+          if (d < vd) acc[i][c] = fmaf(pj, to_float(v_s[j * vd + d]), acc[i][c]);
         }
       }
     }
@@ -173,19 +193,26 @@ paged_attention_simt_kernel(const AttentionArgs a) {
     if (p >= n_pairs) continue;
     const int qi = p / n_heads, hj = p - qi * n_heads;
     const int head = kvh * g + chunk * a.heads_per_chunk + hj;
-    const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;   // a fully masked row gives zeros
+    float denominator = l[i], keep = 1.0f;
+    if (a.sinks != nullptr) {
+      // The sink joins the sum as one more exponential: rescale to the larger of the two maxima.
+      const float sink = a.sinks[head], top = fmaxf(m[i], sink);
+      keep = expf(m[i] - top);
+      denominator = l[i] * keep + expf(sink - top);
+    }
+    const float inv = denominator > 0.0f ? keep / denominator : 0.0f;   // a fully masked row gives zeros
 #pragma unroll
     for (int c = 0; c < ACC; ++c) {
       const int d = lane + 32 * c;
-      if (d < hd) out[(static_cast<size_t>(tok0 + qi) * a.nh + head) * hd + d] = from_float<T>(acc[i][c] * inv);
+      if (d < vd) out[(static_cast<size_t>(tok0 + qi) * a.nh + head) * vd + d] = from_float<T>(acc[i][c] * inv);
     }
   }
 }
 
 template <typename T, int ACC>
 int attention_simt_launch(const AttentionArgs& a, int n_tiles, int head_chunks, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(ATT_MAX_PAIRS) * a.hd * sizeof(float) +
-                      static_cast<size_t>(ATT_TILE) * (2 * a.hd + KPad<T>::N) * sizeof(T);
+  const size_t smem = static_cast<size_t>(ATT_MAX_PAIRS) * a.kd * sizeof(float) +
+                      static_cast<size_t>(ATT_TILE) * (a.kd + a.vd + KPad<T>::N) * sizeof(T);
   auto kernel = paged_attention_simt_kernel<T, ACC>;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -196,7 +223,7 @@ int attention_simt_launch(const AttentionArgs& a, int n_tiles, int head_chunks, 
 
 template <typename T>
 int attention_simt_dispatch(const AttentionArgs& a, int n_tiles, int head_chunks, cudaStream_t stream) {
-  switch ((a.hd + 31) / 32) {
+  switch ((a.vd + 31) / 32) {
     case 1: return attention_simt_launch<T, 1>(a, n_tiles, head_chunks, stream);
     case 2: return attention_simt_launch<T, 2>(a, n_tiles, head_chunks, stream);
     case 3: return attention_simt_launch<T, 3>(a, n_tiles, head_chunks, stream);
@@ -225,11 +252,13 @@ ZB_API int zb_attention_simt_tile_tokens(int group) {
 ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cache, const int* block_table,
                                    int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
                                    const int* tile_q0, int n_tiles, int tile_tokens, const int* row_q_start,
-                                   const int* row_q_len, const int* row_ctx, int nh, int nkv, int hd, int window,
-                                   float scale, const float* head_slopes, int dtype, int* status, void* stream) {
-  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0)
+                                   const int* row_q_len, const int* row_ctx, int nh, int nkv, int kd, int vd,
+                                   int window, int chunk, float scale, const float* head_slopes, const float* sinks,
+                                   int dtype, int* status, void* stream) {
+  if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || kd <= 0 || vd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0 ||
+      chunk < 0)
     return ERR_BAD_ARGUMENT;
-  if (hd % 16 != 0 || hd > 256) return ERR_UNSUPPORTED;
+  if (kd % 2 != 0 || kd > 256 || vd > 256) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   const int g = nh / nkv;
   const int heads_per_chunk = g < ATT_MAX_PAIRS ? g : ATT_MAX_PAIRS;
@@ -240,8 +269,9 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   a.tile_row = tile_row; a.tile_q0 = tile_q0;
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
-  a.nh = nh; a.nkv = nkv; a.hd = hd; a.window = window; a.tile_tokens = tile_tokens;
-  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.head_slopes = head_slopes; a.status = status;
+  a.nh = nh; a.nkv = nkv; a.kd = kd; a.vd = vd; a.window = window; a.chunk = chunk; a.tile_tokens = tile_tokens;
+  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.head_slopes = head_slopes; a.sinks = sinks;
+  a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   return dtype == DTYPE_F32 ? attention_simt_dispatch<float>(a, n_tiles, head_chunks, s)
                             : attention_simt_dispatch<__nv_bfloat16>(a, n_tiles, head_chunks, s);

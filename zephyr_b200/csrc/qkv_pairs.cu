@@ -1,0 +1,160 @@
+// From a fused q/k/v projection to queries and cache entries, for attention whose rotation turns
+// adjacent pairs: bias, per-head RMS norm of q and k, rotation, and the write of k and v into the
+// pages, in one pass and in float32 with a single rounding at the store.
+//
+//   x = projection + bias                                  (q, k and v)
+//   x = x / sqrt(mean(x^2) + eps) * w                      (q and k; w shared by the heads)
+//   (x[2i], x[2i+1]) <- (x[2i] c - x[2i+1] s, x[2i+1] c + x[2i] s),  c, s = cos, sin(p * f[i])
+//                                                          (q and k; i < rot_dims / 2, the rest passes)
+//
+// with p the token's position and f a table of float32 frequencies the host made.  Keys and values
+// may differ in width: a page holds [nkv][page_size][kd] keys and behind them [nkv][page_size][vd]
+// values; rows whose bytes are a multiple of 16 are stored with permuted 16-byte chunks (common.cuh:
+// kv_swizzle), any other width as it is.  One warp per (token, head); a lane owns adjacent pairs.
+#include "common.cuh"
+
+namespace zb {
+
+constexpr int QP_WARPS = 4;
+constexpr int QP_PAIRS = 4;        // pairs per lane: widths up to 256
+
+struct QkvPairsArgs {
+  void* q_out;               // [T, nh * kd]
+  const void* qkv;           // [T, stride]: q heads, k heads, v heads
+  long long stride;
+  const float* bias;         // null or [nh*kd + nkv*kd + nkv*vd]
+  const float* q_norm_w;     // null or [kd]
+  const float* k_norm_w;     // null or [kd]
+  float eps;
+  const float* freqs;        // null or [rot_dims / 2]
+  int rot_dims;
+  const int* positions;
+  const int* token_row;
+  void* cache;               // null: only the queries are made
+  const int* block_table;
+  int max_blocks, page_size, num_pages, num_rows;
+  int nh, nkv, kd, vd;
+  int* status;
+};
+
+template <typename IN, typename T>
+__global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairsArgs a) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * QP_WARPS + (threadIdx.x >> 5);
+  const int total = a.cache != nullptr ? a.nh + 2 * a.nkv : a.nh;
+  if (head >= total) return;
+  const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
+  const int dim = (is_q || is_k) ? a.kd : a.vd;
+  const long long col = is_q ? static_cast<long long>(head) * a.kd
+                      : is_k ? static_cast<long long>(a.nh) * a.kd + static_cast<long long>(head - a.nh) * a.kd
+                             : static_cast<long long>(a.nh + a.nkv) * a.kd +
+                                   static_cast<long long>(head - a.nh - a.nkv) * a.vd;
+  const IN* src = static_cast<const IN*>(a.qkv) + static_cast<long long>(t) * a.stride + col;
+  const int pos = a.positions[t];
+
+  float x[QP_PAIRS][2];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < QP_PAIRS; ++k) {
+    const int i = 2 * (lane + 32 * k);
+    x[k][0] = x[k][1] = 0.0f;
+    if (i < dim) {
+      x[k][0] = to_float(src[i]) + (a.bias != nullptr ? a.bias[col + i] : 0.0f);
+      if (i + 1 < dim) x[k][1] = to_float(src[i + 1]) + (a.bias != nullptr ? a.bias[col + i + 1] : 0.0f);
+      ss += x[k][0] * x[k][0] + x[k][1] * x[k][1];
+    }
+  }
+  {
+    const float* w = is_q ? a.q_norm_w : (is_k ? a.k_norm_w : nullptr);
+    if (w != nullptr) {
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(dim) + a.eps);
+#pragma unroll
+      for (int k = 0; k < QP_PAIRS; ++k) {
+        const int i = 2 * (lane + 32 * k);
+        if (i < dim) {
+          x[k][0] = x[k][0] * inv * w[i];
+          if (i + 1 < dim) x[k][1] = x[k][1] * inv * w[i + 1];
+        }
+      }
+    }
+  }
+  if ((is_q || is_k) && a.freqs != nullptr) {
+#pragma unroll
+    for (int k = 0; k < QP_PAIRS; ++k) {
+      const int i = 2 * (lane + 32 * k);
+      if (i + 1 < a.rot_dims) {
+        float s, c;
+        sincosf(static_cast<float>(pos) * a.freqs[i >> 1], &s, &c);
+        const float u = x[k][0], v = x[k][1];
+        x[k][0] = u * c - v * s;
+        x[k][1] = v * c + u * s;
+      }
+    }
+  }
+
+  T* dst;
+  int swizzle_pos = -1;          // -1: the row is stored as it is
+  if (is_q) {
+    dst = static_cast<T*>(a.q_out) + (static_cast<long long>(t) * a.nh + head) * a.kd;
+  } else {
+    const int row = a.token_row[t], block = pos / a.page_size;
+    if (row < 0 || row >= a.num_rows || block >= a.max_blocks) {
+      if (lane == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, row, t);
+      return;
+    }
+    const int page = a.block_table[static_cast<long long>(row) * a.max_blocks + block];
+    if (page <= 0 || page >= a.num_pages) {      // page 0 is the null page and is never written
+      if (lane == 0) report(a.status, STATUS_PAGE_OUT_OF_RANGE, page, t);
+      return;
+    }
+    const int kvh = is_k ? head - a.nh : head - a.nh - a.nkv;
+    const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (a.kd + a.vd);
+    const long long part = is_k ? 0 : static_cast<long long>(a.nkv) * a.page_size * a.kd;
+    dst = static_cast<T*>(a.cache) + static_cast<long long>(page) * page_elems + part +
+          (static_cast<long long>(kvh) * a.page_size + pos % a.page_size) * dim;
+    if ((dim * static_cast<int>(sizeof(T))) % 16 == 0) swizzle_pos = pos;
+  }
+#pragma unroll
+  for (int k = 0; k < QP_PAIRS; ++k) {
+    const int i = 2 * (lane + 32 * k);
+    if (i < dim) {
+      const int at = swizzle_pos >= 0 ? kv_element_index(i, swizzle_pos, dim, sizeof(T)) : i;
+      dst[at] = from_float<T>(x[k][0]);
+      if (i + 1 < dim) dst[at + 1] = from_float<T>(x[k][1]);     // a pair never straddles a 16-byte chunk
+    }
+  }
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const float* bias, const float* q_norm_w,
+                        const float* k_norm_w, float eps, const float* freqs, int rot_dims, const int* positions,
+                        const int* token_row, void* cache, const int* block_table, int max_blocks, int page_size,
+                        int num_pages, int num_rows, int tokens, int nh, int nkv, int kd, int vd, int in_dtype,
+                        int dtype, int* status, void* stream) {
+  if (tokens < 0 || nh <= 0 || nkv <= 0 || kd <= 0 || vd <= 0 || rot_dims < 0 || rot_dims > kd || rot_dims % 2 != 0 ||
+      page_size <= 0)
+    return ERR_BAD_ARGUMENT;
+  if (kd > 64 * QP_PAIRS || vd > 64 * QP_PAIRS) return ERR_UNSUPPORTED;
+  if (tokens == 0) return OK;
+  QkvPairsArgs a;
+  a.q_out = q_out; a.qkv = qkv; a.stride = stride; a.bias = bias; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w;
+  a.eps = eps; a.freqs = freqs; a.rot_dims = freqs != nullptr ? rot_dims : 0; a.positions = positions;
+  a.token_row = token_row; a.cache = cache; a.block_table = block_table; a.max_blocks = max_blocks;
+  a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows; a.nh = nh; a.nkv = nkv; a.kd = kd;
+  a.vd = vd; a.status = status;
+  const int heads = cache != nullptr ? nh + 2 * nkv : nh;
+  const dim3 grid(tokens, (heads + QP_WARPS - 1) / QP_WARPS);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32) {
+    if (in_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
+    qkv_pairs_kernel<float, float><<<grid, QP_WARPS * 32, 0, s>>>(a);
+  } else if (in_dtype == DTYPE_F32) {
+    qkv_pairs_kernel<float, __nv_bfloat16><<<grid, QP_WARPS * 32, 0, s>>>(a);
+  } else {
+    qkv_pairs_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, QP_WARPS * 32, 0, s>>>(a);
+  }
+  return launch_result();
+}

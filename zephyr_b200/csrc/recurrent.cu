@@ -1,0 +1,483 @@
+// Layers that carry a state of fixed size from token to token, and the norms around them.
+//
+//   * layer norm with scale and shift, alone and fused with the residual sum: the residual stream is
+//     float32; r += m * LN_post(delta), then y = LN_pre(r), in one pass over the row;
+//   * a table lookup that writes float32 rows (the start of a float32 residual stream);
+//   * the causal convolution over a few taps per channel with its SiLU, whose last taps - 1 inputs
+//     live in the request's state slot;
+//   * the decayed outer-product recurrence  S_t = diag(a_t) S_{t-1} + k_t v_t^T,  o_t = S_t^T q_t
+//     per head, S [D, V] float32 in the request's state slot, in two settings: a decay per key channel
+//     a = sigmoid(z)^(1/tau) (gated linear attention), and one decay per head a = exp(-exp(A) dt)
+//     with k = dt B, q = C and a skip term D x (the state-space form of Mamba-2);
+//   * the RMS norm over equal groups of a row with a SiLU gate before or behind it.
+//
+// Everything that enters the recurrence is float32: decays, their logarithms, softplus, step sizes,
+// the state, the sums.  A row's tokens are run in their order, so a result does not depend on how a
+// prompt was cut into steps or on what else a step carries.
+#include "common.cuh"
+
+namespace zb {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+// ------------------------------------------------------------------------------------------------
+// Layer norm.  One CTA per row; the row sits in shared memory as float32, mean and variance are
+// two passes over it (the variance is the mean of the squared deviations).
+__device__ __forceinline__ void layer_norm_stats(const float* row, int H, float eps, float* scratch, float& mean,
+                                                 float& rstd) {
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) s += row[i];
+  mean = block_sum(s, scratch) / static_cast<float>(H);
+  float v = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float d = row[i] - mean;
+    v = fmaf(d, d, v);
+  }
+  rstd = 1.0f / sqrtf(block_sum(v, scratch) / static_cast<float>(H) + eps);
+}
+
+template <typename X, typename T>
+__global__ void layer_norm_kernel(T* out, const X* x, const void* w, const void* b, int w_dtype, float eps, int H) {
+  extern __shared__ __align__(16) float ln_row[];
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ln_row[i] = to_float(x[base + i]);
+  __syncthreads();
+  float mean, rstd;
+  layer_norm_stats(ln_row, H, eps, scratch, mean, rstd);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w, w_dtype, i), load_scale(b, w_dtype, i)));
+}
+
+// residual += mult * LN(delta; w1, b1); then, if `out`, out = LN(residual; w2, b2).
+template <typename T>
+__global__ void residual_layer_norm_kernel(float* residual, const T* delta, const void* w1, const void* b1, float mult,
+                                           T* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
+                                           int H) {
+  extern __shared__ __align__(16) float ln_row[];
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ln_row[i] = to_float(delta[base + i]);
+  __syncthreads();
+  float mean, rstd;
+  layer_norm_stats(ln_row, H, eps1, scratch, mean, rstd);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float y = fmaf((ln_row[i] - mean) * rstd, load_scale(w1, w_dtype, i), load_scale(b1, w_dtype, i));
+    const float r = fmaf(mult, y, residual[base + i]);
+    residual[base + i] = r;
+    ln_row[i] = r;              // each thread rewrites only the elements it read
+  }
+  if (out == nullptr) return;
+  __syncthreads();
+  layer_norm_stats(ln_row, H, eps2, scratch, mean, rstd);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w2, w_dtype, i), load_scale(b2, w_dtype, i)));
+}
+
+template <typename T>
+__global__ void embedding_f32_kernel(float* out, const T* table, const int* ids, int H, int V, int* status) {
+  const int t = blockIdx.x, id = ids[t];
+  if (id < 0 || id >= V) {
+    if (threadIdx.x == 0) report(status, STATUS_TOKEN_OUT_OF_RANGE, id, t);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(t) * H + i] = 0.0f;
+    return;
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[static_cast<size_t>(t) * H + i] = to_float(table[static_cast<size_t>(id) * H + i]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Causal convolution per channel with SiLU.  A thread owns a channel of one request and walks that
+// request's new tokens in order with the last `taps` inputs in registers; the window starts from the
+// request's state (zeros for a new request) and its last taps - 1 inputs go back there.
+constexpr int CONV_MAX_TAPS = 8;
+
+struct ConvArgs {
+  void* out;                 // [tokens, C]
+  const void* x;             // [tokens, x_stride], channel c at column c
+  long long x_stride;
+  float* state;              // slot s at state + s * slot_stride: [taps - 1][C], oldest input first
+  long long slot_stride;
+  const int* slots;
+  const int* row_q_start;
+  const int* row_q_len;
+  const void* w;             // [C, taps], the last column weighs the current token
+  const void* bias;          // [C]
+  int w_dtype, C, taps, num_slots, write_state;
+  int* status;
+};
+
+template <typename T>
+__global__ void causal_conv_silu_kernel(const ConvArgs a) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (c >= a.C) return;
+  const int slot = a.slots[row];
+  if (slot < 0 || slot >= a.num_slots) {
+    report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+    return;
+  }
+  const int first = CONV_MAX_TAPS - a.taps;          // window entries before `first` stay zero
+  float win[CONV_MAX_TAPS], w[CONV_MAX_TAPS];
+  float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+    w[j] = j >= first ? load_scale(a.w, a.w_dtype, c * a.taps + (j - first)) : 0.0f;
+    // win[j + 1] is what win[j] will be after the first shift
+    win[j] = (j > first) ? state[static_cast<long long>(j - first - 1) * a.C + c] : 0.0f;
+  }
+  const float bias = load_scale(a.bias, a.w_dtype, c);
+  const T* x = static_cast<const T*>(a.x);
+  T* out = static_cast<T*>(a.out);
+  const int t0 = a.row_q_start[row], n = a.row_q_len[row];
+  for (int i = 0; i < n; ++i) {
+#pragma unroll
+    for (int j = 0; j + 1 < CONV_MAX_TAPS; ++j) win[j] = win[j + 1];
+    win[CONV_MAX_TAPS - 1] = to_float(x[static_cast<long long>(t0 + i) * a.x_stride + c]);
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) acc = fmaf(w[j], win[j], acc);
+    out[static_cast<long long>(t0 + i) * a.C + c] = from_float<T>(silu_f(acc + bias));
+  }
+  if (a.write_state) {
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+      if (j > first) state[static_cast<long long>(j - first - 1) * a.C + c] = win[j];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// The recurrence.  A CTA owns one request, one head and 32 value columns; warp w owns the key
+// channels 32 w .. 32 w + 31 of those columns, each lane one column with its 32 state values in
+// registers.  The tokens of the request are taken SCAN_CHUNK at a time: decays, keys, queries and
+// values of the chunk are formed in shared memory (all float32), every warp runs the chunk's tokens
+// in order, and the warps' partial outputs are added in warp order.
+constexpr int SCAN_CHUNK = 8;
+constexpr int SCAN_ROWS = 32;        // key channels per warp
+constexpr int SCAN_COLS = 32;        // value columns per CTA
+
+constexpr int SCAN_GATED = 0;        // a[d] = sigmoid(z[d] + bias[d])^(1/tau), q scaled
+constexpr int SCAN_STATE_SPACE = 1;  // a = exp(-exp(A_log[h]) dt), k = dt B, q = C, o += skip[h] v, dt = softplus(. + dt_bias[h])
+
+struct ScanArgs {
+  const void* q; long long q_stride;   // [tokens, .]: head h (or its group) at column h * D
+  const void* k; long long k_stride;
+  const void* v; long long v_stride;   // [tokens, .]: head h at column h * V
+  const float* z; long long z_stride;  // gated: decay logits [tokens, H * D], float32
+  const void* z_bias;                  // gated: [H * D]
+  const void* dt; long long dt_stride; // state space: [tokens, H]
+  const void* dt_bias; const void* a_log; const void* skip;   // state space: [H] each
+  int w_dtype;
+  float* state; long long slot_stride; // slot s at state + s * slot_stride: [H][D][V]
+  float* out;                          // [tokens, H * V] float32
+  const int* slots; const int* row_q_start; const int* row_q_len;
+  int H, D, V, heads_per_group, num_slots, write_state;
+  float q_scale, inv_tau;
+  int* status;
+};
+
+template <typename T, int MODE>
+__global__ void __launch_bounds__(256) decayed_state_scan_kernel(const ScanArgs a) {
+  extern __shared__ __align__(16) float scan_smem[];
+  const int D = a.D, V = a.V, nwarps = blockDim.x >> 5, Dp = nwarps * SCAN_ROWS;
+  float* a_s = scan_smem;                                   // [SCAN_CHUNK][Dp] (state space: one value per token)
+  float* k_s = a_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][Dp]
+  float* q_s = k_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][Dp]
+  float* v_s = q_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][SCAN_COLS]
+  float* o_s = v_s + SCAN_CHUNK * SCAN_COLS;                // [SCAN_CHUNK][nwarps][SCAN_COLS]
+  const int v0 = blockIdx.x * SCAN_COLS, h = blockIdx.y, row = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = a.slots[row];
+  if (slot < 0 || slot >= a.num_slots) {
+    if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+    return;
+  }
+  const int t0 = a.row_q_start[row], n = a.row_q_len[row];
+  const int col = v0 + lane, d0 = warp * SCAN_ROWS;
+  float* state = a.state + static_cast<long long>(slot) * a.slot_stride + static_cast<long long>(h) * D * V;
+  float S[SCAN_ROWS];
+#pragma unroll
+  for (int d = 0; d < SCAN_ROWS; ++d)
+    S[d] = (d0 + d < D && col < V) ? state[static_cast<long long>(d0 + d) * V + col] : 0.0f;
+
+  const T* qp = static_cast<const T*>(a.q);
+  const T* kp = static_cast<const T*>(a.k);
+  const T* vp = static_cast<const T*>(a.v);
+  const int qk_col = (MODE == SCAN_STATE_SPACE ? h / a.heads_per_group : h) * D;
+  float head_decay = 0.0f, head_dt_bias = 0.0f, head_skip = 0.0f;
+  if (MODE == SCAN_STATE_SPACE) {
+    head_decay = -expf(load_scale(a.a_log, a.w_dtype, h));
+    head_dt_bias = load_scale(a.dt_bias, a.w_dtype, h);
+    head_skip = load_scale(a.skip, a.w_dtype, h);
+  }
+
+  for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+    const int nc = min(SCAN_CHUNK, n - c0);
+    __syncthreads();                      // the chunk before is no longer read
+    for (int e = threadIdx.x; e < SCAN_CHUNK * Dp; e += blockDim.x) {
+      const int t = e / Dp, d = e - t * Dp;
+      float av = 0.0f, kv = 0.0f, qv = 0.0f;
+      if (t < nc && d < D) {
+        const long long tok = t0 + c0 + t;
+        kv = to_float(kp[tok * a.k_stride + qk_col + d]);
+        qv = to_float(qp[tok * a.q_stride + qk_col + d]);
+        if (MODE == SCAN_GATED) {
+          const float z = a.z[tok * a.z_stride + h * D + d] + load_scale(a.z_bias, a.w_dtype, h * D + d);
+          av = expf(log_sigmoid_f(z) * a.inv_tau);
+          qv *= a.q_scale;
+        } else {
+          const float dt = softplus_f(to_float(static_cast<const T*>(a.dt)[tok * a.dt_stride + h]) + head_dt_bias);
+          av = expf(head_decay * dt);
+          kv *= dt;
+        }
+      }
+      a_s[e] = av;
+      k_s[e] = kv;
+      q_s[e] = qv;
+    }
+    for (int e = threadIdx.x; e < SCAN_CHUNK * SCAN_COLS; e += blockDim.x) {
+      const int t = e / SCAN_COLS, c = v0 + (e - t * SCAN_COLS);
+      v_s[e] = (t < nc && c < V) ? to_float(vp[static_cast<long long>(t0 + c0 + t) * a.v_stride + h * V + c]) : 0.0f;
+    }
+    __syncthreads();
+    for (int t = 0; t < nc; ++t) {
+      const float vt = v_s[t * SCAN_COLS + lane];
+      const float* at = a_s + t * Dp + d0;
+      const float* kt = k_s + t * Dp + d0;
+      const float* qt = q_s + t * Dp + d0;
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+#pragma unroll
+      for (int d = 0; d < SCAN_ROWS; d += 4) {
+        S[d] = fmaf(at[d], S[d], kt[d] * vt);
+        o0 = fmaf(S[d], qt[d], o0);
+        S[d + 1] = fmaf(at[d + 1], S[d + 1], kt[d + 1] * vt);
+        o1 = fmaf(S[d + 1], qt[d + 1], o1);
+        S[d + 2] = fmaf(at[d + 2], S[d + 2], kt[d + 2] * vt);
+        o2 = fmaf(S[d + 2], qt[d + 2], o2);
+        S[d + 3] = fmaf(at[d + 3], S[d + 3], kt[d + 3] * vt);
+        o3 = fmaf(S[d + 3], qt[d + 3], o3);
+      }
+      o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < nc * SCAN_COLS; e += blockDim.x) {
+      const int t = e / SCAN_COLS, l = e - t * SCAN_COLS, c = v0 + l;
+      if (c >= V) continue;
+      float o = 0.0f;
+      for (int w = 0; w < nwarps; ++w) o += o_s[(t * nwarps + w) * SCAN_COLS + l];
+      if (MODE == SCAN_STATE_SPACE) o = fmaf(head_skip, v_s[t * SCAN_COLS + l], o);
+      a.out[static_cast<long long>(t0 + c0 + t) * a.H * V + h * V + c] = o;
+    }
+  }
+  if (a.write_state) {
+#pragma unroll
+    for (int d = 0; d < SCAN_ROWS; ++d)
+      if (d0 + d < D && col < V) state[static_cast<long long>(d0 + d) * V + col] = S[d];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMS norm over equal groups of a float32 row with a SiLU gate: y = unit_rms(o * silu(g)) * w when the
+// gate comes first, y = unit_rms(o) * w * silu(g) otherwise.  w has `w_len` entries and is used
+// periodically (a scale per column, or one scale vector shared by all groups).  One warp per group.
+template <typename T>
+__global__ void gated_group_rms_norm_kernel(T* out, const float* o, const T* gate, long long gate_stride, const void* w,
+                                            int w_dtype, int w_len, int width, int group, float eps, int gate_first,
+                                            int tokens) {
+  const int groups = width / group;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(tokens) * groups) return;
+  const int lane = threadIdx.x & 31;
+  const long long t = item / groups;
+  const int c0 = static_cast<int>(item - t * groups) * group;
+  float ss = 0.0f;
+  for (int i = lane; i < group; i += 32) {
+    float val = o[t * width + c0 + i];
+    if (gate_first) val *= silu_f(to_float(gate[t * gate_stride + c0 + i]));
+    ss = fmaf(val, val, ss);
+  }
+  const float r = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(group) + eps);
+  for (int i = lane; i < group; i += 32) {
+    const float g = silu_f(to_float(gate[t * gate_stride + c0 + i]));
+    float val = o[t * width + c0 + i];
+    if (gate_first) val *= g;
+    val = val * r * load_scale(w, w_dtype, (c0 + i) % w_len);
+    if (!gate_first) val *= g;
+    out[t * width + c0 + i] = from_float<T>(val);
+  }
+}
+
+// out = sa * a + sb * b, float32 arithmetic, one rounding; a and b may be float32 whatever out is.
+template <typename IN, typename T>
+__global__ void scaled_sum_kernel(T* out, const IN* a, const IN* b, float sa, float sb, long long n) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_float<T>(fmaf(sa, to_float(a[i]), sb * to_float(b[i])));
+}
+
+inline int norm_threads(int H) { return H >= 2048 ? 512 : (H >= 512 ? 256 : 128); }
+
+template <typename K>
+inline int allow_shared(K kernel, size_t bytes) {
+  if (bytes > 227 * 1024) return ERR_UNSUPPORTED;
+  if (bytes > 48 * 1024 &&
+      cuda_failed(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes))))
+    return ERR_CUDA;
+  return OK;
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+// out [rows, H] (out_dtype) = LN(x [rows, H] (x_dtype)); scale and shift in w_dtype.
+ZB_API int zb_layer_norm(void* out, const void* x, const void* w, const void* b, int w_dtype, float eps, int rows,
+                         int H, int x_dtype, int out_dtype, void* stream) {
+  if (rows < 0 || H <= 0) return ERR_BAD_ARGUMENT;
+  if (rows == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const size_t smem = static_cast<size_t>(H) * sizeof(float);
+  const int threads = norm_threads(H);
+#define ZB_LN(X, T)                                                                                    \
+  {                                                                                                    \
+    auto kernel = layer_norm_kernel<X, T>;                                                             \
+    if (int rc = allow_shared(kernel, smem)) return rc;                                                \
+    kernel<<<rows, threads, smem, s>>>(static_cast<T*>(out), static_cast<const X*>(x), w, b, w_dtype, eps, H); \
+  }
+  if (x_dtype == DTYPE_F32 && out_dtype == DTYPE_F32) ZB_LN(float, float)
+  else if (x_dtype == DTYPE_F32) ZB_LN(float, __nv_bfloat16)
+  else if (out_dtype == DTYPE_F32) ZB_LN(__nv_bfloat16, float)
+  else ZB_LN(__nv_bfloat16, __nv_bfloat16)
+#undef ZB_LN
+  return launch_result();
+}
+
+ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void* w1, const void* b1, float mult,
+                                  void* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
+                                  int rows, int H, int dtype, void* stream) {
+  if (rows < 0 || H <= 0) return ERR_BAD_ARGUMENT;
+  if (rows == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const size_t smem = static_cast<size_t>(H) * sizeof(float);
+  const int threads = norm_threads(H);
+  if (dtype == DTYPE_F32) {
+    auto kernel = residual_layer_norm_kernel<float>;
+    if (int rc = allow_shared(kernel, smem)) return rc;
+    kernel<<<rows, threads, smem, s>>>(residual, static_cast<const float*>(delta), w1, b1, mult,
+                                       static_cast<float*>(out), w2, b2, w_dtype, eps1, eps2, H);
+  } else {
+    auto kernel = residual_layer_norm_kernel<__nv_bfloat16>;
+    if (int rc = allow_shared(kernel, smem)) return rc;
+    kernel<<<rows, threads, smem, s>>>(residual, static_cast<const __nv_bfloat16*>(delta), w1, b1, mult,
+                                       static_cast<__nv_bfloat16*>(out), w2, b2, w_dtype, eps1, eps2, H);
+  }
+  return launch_result();
+}
+
+ZB_API int zb_embedding_f32(float* out, const void* table, const int* ids, int tokens, int H, int V, int dtype,
+                            int* status, void* stream) {
+  if (tokens < 0 || H <= 0 || V <= 0) return ERR_BAD_ARGUMENT;
+  if (tokens == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32)
+    embedding_f32_kernel<float><<<tokens, 128, 0, s>>>(out, static_cast<const float*>(table), ids, H, V, status);
+  else
+    embedding_f32_kernel<__nv_bfloat16><<<tokens, 128, 0, s>>>(out, static_cast<const __nv_bfloat16*>(table), ids, H, V,
+                                                               status);
+  return launch_result();
+}
+
+ZB_API int zb_causal_conv_silu(void* out, const void* x, long long x_stride, float* state, long long slot_stride,
+                               const int* slots, const int* row_q_start, const int* row_q_len, int rows, const void* w,
+                               const void* bias, int w_dtype, int C, int taps, int num_slots, int write_state, int dtype,
+                               int* status, void* stream) {
+  if (rows < 0 || C <= 0 || taps <= 0) return ERR_BAD_ARGUMENT;
+  if (taps > CONV_MAX_TAPS) return ERR_UNSUPPORTED;
+  if (rows == 0) return OK;
+  ConvArgs a;
+  a.out = out; a.x = x; a.x_stride = x_stride; a.state = state; a.slot_stride = slot_stride; a.slots = slots;
+  a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.w = w; a.bias = bias; a.w_dtype = w_dtype; a.C = C;
+  a.taps = taps; a.num_slots = num_slots; a.write_state = write_state; a.status = status;
+  auto s = static_cast<cudaStream_t>(stream);
+  const dim3 grid((C + 127) / 128, rows);
+  if (dtype == DTYPE_F32) causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>(a);
+  else causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a);
+  return launch_result();
+}
+
+// The most key channels a head of the recurrence may have.
+ZB_API int zb_state_scan_max_channels() { return 8 * SCAN_ROWS; }
+
+ZB_API int zb_decayed_state_scan(float* out, const void* q, long long q_stride, const void* k, long long k_stride,
+                                 const void* v, long long v_stride, const float* z, long long z_stride,
+                                 const void* z_bias, const void* dt, long long dt_stride, const void* dt_bias,
+                                 const void* a_log, const void* skip, int w_dtype, float* state, long long slot_stride,
+                                 const int* slots, const int* row_q_start, const int* row_q_len, int rows, int H, int D,
+                                 int V, int heads_per_group, int num_slots, int write_state, float q_scale,
+                                 float inv_tau, int mode, int dtype, int* status, void* stream) {
+  if (rows < 0 || H <= 0 || D <= 0 || V <= 0 || heads_per_group <= 0) return ERR_BAD_ARGUMENT;
+  if (D > 8 * SCAN_ROWS) return ERR_UNSUPPORTED;
+  if (mode != SCAN_GATED && mode != SCAN_STATE_SPACE) return ERR_BAD_ARGUMENT;
+  if (rows == 0) return OK;
+  ScanArgs a;
+  a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
+  a.z = z; a.z_stride = z_stride; a.z_bias = z_bias; a.dt = dt; a.dt_stride = dt_stride; a.dt_bias = dt_bias;
+  a.a_log = a_log; a.skip = skip; a.w_dtype = w_dtype; a.state = state; a.slot_stride = slot_stride; a.out = out;
+  a.slots = slots; a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.H = H; a.D = D; a.V = V;
+  a.heads_per_group = heads_per_group; a.num_slots = num_slots; a.write_state = write_state; a.q_scale = q_scale;
+  a.inv_tau = inv_tau; a.status = status;
+  const int warps = (D + SCAN_ROWS - 1) / SCAN_ROWS;
+  const size_t smem = sizeof(float) * (3 * SCAN_CHUNK * warps * SCAN_ROWS + SCAN_CHUNK * SCAN_COLS +
+                                       SCAN_CHUNK * warps * SCAN_COLS);
+  const dim3 grid((V + SCAN_COLS - 1) / SCAN_COLS, H, rows);
+  auto s = static_cast<cudaStream_t>(stream);
+#define ZB_SCAN(T, MODE) decayed_state_scan_kernel<T, MODE><<<grid, warps * 32, smem, s>>>(a)
+  if (dtype == DTYPE_F32) {
+    if (mode == SCAN_GATED) ZB_SCAN(float, SCAN_GATED); else ZB_SCAN(float, SCAN_STATE_SPACE);
+  } else {
+    if (mode == SCAN_GATED) ZB_SCAN(__nv_bfloat16, SCAN_GATED); else ZB_SCAN(__nv_bfloat16, SCAN_STATE_SPACE);
+  }
+#undef ZB_SCAN
+  return launch_result();
+}
+
+ZB_API int zb_gated_group_rms_norm(void* out, const float* o, const void* gate, long long gate_stride, const void* w,
+                                   int w_dtype, int w_len, int tokens, int width, int group, float eps, int gate_first,
+                                   int dtype, void* stream) {
+  if (tokens < 0 || width <= 0 || group <= 0 || width % group != 0 || w_len <= 0) return ERR_BAD_ARGUMENT;
+  if (tokens == 0) return OK;
+  const long long items = static_cast<long long>(tokens) * (width / group);
+  const int warps = 4;
+  const unsigned blocks = static_cast<unsigned>((items + warps - 1) / warps);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (dtype == DTYPE_F32)
+    gated_group_rms_norm_kernel<float><<<blocks, warps * 32, 0, s>>>(
+        static_cast<float*>(out), o, static_cast<const float*>(gate), gate_stride, w, w_dtype, w_len, width, group, eps,
+        gate_first, tokens);
+  else
+    gated_group_rms_norm_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, s>>>(
+        static_cast<__nv_bfloat16*>(out), o, static_cast<const __nv_bfloat16*>(gate), gate_stride, w, w_dtype, w_len,
+        width, group, eps, gate_first, tokens);
+  return launch_result();
+}
+
+ZB_API int zb_scaled_sum(void* out, const void* a, const void* b, float sa, float sb, long long n, int in_dtype,
+                         int dtype, void* stream) {
+  if (n < 0) return ERR_BAD_ARGUMENT;
+  if (n == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+  using bf16 = __nv_bfloat16;
+  if (in_dtype == DTYPE_F32 && dtype == DTYPE_F32)
+    scaled_sum_kernel<float, float><<<blocks, 256, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(a),
+                                                           static_cast<const float*>(b), sa, sb, n);
+  else if (in_dtype == DTYPE_F32)
+    scaled_sum_kernel<float, bf16><<<blocks, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const float*>(a),
+                                                          static_cast<const float*>(b), sa, sb, n);
+  else if (dtype == DTYPE_BF16)
+    scaled_sum_kernel<bf16, bf16><<<blocks, 256, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(a),
+                                                         static_cast<const bf16*>(b), sa, sb, n);
+  else
+    return ERR_BAD_ARGUMENT;
+  return launch_result();
+}

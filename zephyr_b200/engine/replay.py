@@ -23,7 +23,7 @@ from .runner import ModelRunner, StepEntry
 
 class TraceReplayer:
     def __init__(self, model_dir: str | Path, dtype: str, max_tokens: int, page_size: int = 16,
-                 max_requests: int = 8, device: int = 0):
+                 max_requests: int = 4, device: int = 0):
         if max_tokens <= 0:
             raise InvalidArgumentError("max_tokens must be positive")
         if page_size <= 0 or page_size & (page_size - 1) or page_size > 64:
@@ -37,7 +37,10 @@ class TraceReplayer:
         # The pool holds max_tokens tokens; each request's count is rounded up to whole pages by the
         # tables, and 64 is a multiple of every page size allowed here.
         pages = -(-max_tokens // page_size) + 1       # + the null page
-        self.runner = ModelRunner(model, page_size, pages, max_requests)
+        # No request can be longer than the pool: block tables are sized for that, not for the longest
+        # sequence the architecture allows.
+        self.runner = ModelRunner(model, page_size, pages, max_requests,
+                                  max_seq_len=min(spec.max_seq_len, (pages - 1) * page_size))
         self.max_requests = max_requests
 
     def step(self, record: Mapping[str, Any]) -> np.ndarray | None:

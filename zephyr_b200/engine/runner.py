@@ -331,11 +331,14 @@ class ModelRunner:
             ctx = self._context_from(record["device"], sizes, info)
             # One ordinary run first (libraries pick their algorithms and allocate workspaces outside the
             # capture), then the capture, which records the launches without running them.
+            # A recurrent state must not be advanced twice: the slots are put back after the ordinary run.
+            before = self.storage.snapshot_state(self.manager, info["slots"])
             side = torch.cuda.Stream(device=self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):
                 self.model.forward(ctx)
             torch.cuda.current_stream(self.device).wait_stream(side)
+            self.storage.restore_state(self.manager, before)
             graph = torch.cuda.CUDAGraph()
             launched = ops.LAUNCHES
             # All graphs of this runner draw from one pool: they replay one after the other on one stream,

@@ -64,8 +64,25 @@ _SIGNATURES = {
                     c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "zb_attention_simt_tile_tokens": [c_int],
     "zb_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
-                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                c_float, c_void_p, c_int, c_void_p, c_void_p],
+                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "zb_qkv_pairs": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
+                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_void_p, c_void_p],
+    "zb_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_residual_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
+                               c_float, c_float, c_int, c_int, c_int, c_void_p],
+    "zb_embedding_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_causal_conv_silu": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_state_scan_max_channels": [],
+    "zb_decayed_state_scan": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
+                              c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                              c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_float, c_float, c_int, c_int, c_void_p, c_void_p],
+    "zb_gated_group_rms_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_float, c_int, c_int, c_void_p],
+    "zb_scaled_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_longlong, c_int, c_int, c_void_p],
     "zb_paged_decode_supported": [c_int, c_int, c_int, c_int],
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
@@ -330,6 +347,165 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bo
     return out
 
 
+# ------------------------------------------------------- layer norm, recurrences and their norms
+def _f32_vector(v: torch.Tensor | None, size: int, what: str) -> None:
+    _require(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == size),
+             f"{what} must be a contiguous float32 tensor of {size} values")
+
+
+def layer_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
+               out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """(x - mean) / sqrt(var + eps) * w + b over the last dimension of a contiguous [rows, H]; x float32 or
+    bfloat16, the result in ``out_dtype`` (default: x's type); w and b float32."""
+    _cuda(x, w, b)
+    _require(x.dim() == 2 and x.is_contiguous() and x.dtype in DTYPE_CODE, "x must be a contiguous [rows, H]")
+    rows, H = x.shape
+    _f32_vector(w, H, "the scale")
+    _f32_vector(b, H, "the shift")
+    out = torch.empty((rows, H), dtype=out_dtype or x.dtype, device=x.device)
+    _check(library().zb_layer_norm(_ptr(out), _ptr(x), _ptr(w), _ptr(b), 0, float(eps), rows, H, DTYPE_CODE[x.dtype],
+                                   DTYPE_CODE[out.dtype], _stream()), "layer_norm")
+    return out
+
+
+def residual_layer_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, eps1: float,
+                        mult: float, w2: torch.Tensor | None = None, b2: torch.Tensor | None = None,
+                        eps2: float = 0.0) -> torch.Tensor | None:
+    """residual (float32, in place) += mult * LN(delta; w1, b1); with w2 and b2 also returns
+    LN(residual; w2, b2) in delta's type: the sum and the next norm in one pass over the row."""
+    _cuda(residual, delta, w1, b1, w2, b2)
+    _require(residual.dim() == 2 and residual.is_contiguous() and residual.dtype == torch.float32
+             and delta.shape == residual.shape and delta.is_contiguous() and delta.dtype in DTYPE_CODE,
+             "a float32 residual [rows, H] and a summand of the same shape")
+    rows, H = residual.shape
+    for vector in (w1, b1, w2, b2):
+        _f32_vector(vector, H, "scales and shifts")
+    _require((w2 is None) == (b2 is None), "the second norm needs scale and shift")
+    out = torch.empty_like(delta) if w2 is not None else None
+    _check(library().zb_residual_layer_norm(_ptr(residual), _ptr(delta), _ptr(w1), _ptr(b1), float(mult), _ptr(out),
+                                            _ptr(w2), _ptr(b2), 0, float(eps1), float(eps2), rows, H,
+                                            DTYPE_CODE[delta.dtype], _stream()), "residual_layer_norm")
+    return out
+
+
+def embedding_f32(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
+    """Rows of the table as float32 [T, H]: the start of a float32 residual stream."""
+    _cuda(table, ids, status)
+    _i32(ids)
+    _require(table.dim() == 2 and table.is_contiguous() and table.dtype in DTYPE_CODE, "table must be [V, H]")
+    V, H = table.shape
+    out = torch.empty((ids.numel(), H), dtype=torch.float32, device=table.device)
+    _check(library().zb_embedding_f32(_ptr(out), _ptr(table), _ptr(ids), ids.numel(), H, V, DTYPE_CODE[table.dtype],
+                                      _ptr(status), _stream()), "embedding_f32")
+    return out
+
+
+CONV_MAX_TAPS = 8
+
+
+def causal_conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+                     slots: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, status: torch.Tensor,
+                     write_state: bool = True) -> torch.Tensor:
+    """silu(conv(x) + bias) per channel over each row's new tokens; ``x`` [T, >= channels] (rows may be
+    strided), ``w`` float32 [channels, taps] whose last column weighs the current token.  ``state``
+    [slots, (taps - 1) * channels] float32 (rows may be strided) holds every request's last taps - 1
+    inputs, oldest first, and is brought up to date."""
+    _cuda(x, w, bias, state, slots, row_q_start, row_q_len, status)
+    _i32(slots, row_q_start, row_q_len)
+    _require(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= channels and x.dtype in DTYPE_CODE, "x shape")
+    _require(w.dim() == 2 and w.shape[0] == channels and w.dtype == torch.float32 and w.is_contiguous(), "w must be float32 [channels, taps]")
+    taps = w.shape[1]
+    _f32_vector(bias, channels, "the bias")
+    _require(state.dim() == 2 and state.dtype == torch.float32 and state.stride(1) == 1
+             and state.shape[1] == (taps - 1) * channels, "state must be float32 [slots, (taps - 1) * channels]")
+    out = torch.empty((x.shape[0], channels), dtype=x.dtype, device=x.device)
+    _check(library().zb_causal_conv_silu(
+        _ptr(out), _ptr(x), x.stride(0), _ptr(state), state.stride(0), _ptr(slots), _ptr(row_q_start), _ptr(row_q_len),
+        slots.numel(), _ptr(w), _ptr(bias), 0, channels, taps, state.shape[0], int(write_state), DTYPE_CODE[x.dtype],
+        _ptr(status), _stream()), "causal_conv_silu")
+    return out
+
+
+def state_scan_max_channels() -> int:
+    return library().zb_state_scan_max_channels()
+
+
+def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, key_dim: int,
+                       value_dim: int, state: torch.Tensor, slots: torch.Tensor, row_q_start: torch.Tensor,
+                       row_q_len: torch.Tensor, status: torch.Tensor, *, decay_logits: torch.Tensor | None = None,
+                       decay_bias: torch.Tensor | None = None, inv_tau: float = 1.0, q_scale: float = 1.0,
+                       dt: torch.Tensor | None = None, dt_bias: torch.Tensor | None = None,
+                       a_log: torch.Tensor | None = None, skip: torch.Tensor | None = None, heads_per_group: int = 1,
+                       write_state: bool = True) -> torch.Tensor:
+    """S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per head over each row's new tokens, from and
+    to ``state`` [slots, heads * key_dim * value_dim] float32 (rows may be strided); returns o as float32
+    [T, heads * value_dim].  q, k, v: [T, .] with unit inner stride, head h at column h * width.
+    ``mode`` "gated": a = sigmoid(decay_logits + decay_bias)^inv_tau per key channel (logits float32
+    [T, heads * key_dim]), q times ``q_scale``.  ``mode`` "state_space": step = softplus(dt + dt_bias),
+    a = exp(-exp(a_log) step) per head, k times step, o += skip * v; q and k belong to the head's group
+    (head // heads_per_group at column group * key_dim)."""
+    _cuda(q, k, v, state, slots, row_q_start, row_q_len, status, decay_logits, decay_bias, dt, dt_bias, a_log, skip)
+    _i32(slots, row_q_start, row_q_len)
+    T = v.shape[0]
+    for t in (q, k, v):
+        _require(t.dim() == 2 and t.stride(1) == 1 and t.shape[0] == T and t.dtype == v.dtype and t.dtype in DTYPE_CODE,
+                 "q, k and v must be [T, .] of one type with unit inner stride")
+    _require(state.dim() == 2 and state.dtype == torch.float32 and state.stride(1) == 1
+             and state.shape[1] == heads * key_dim * value_dim, "state must be float32 [slots, heads * key_dim * value_dim]")
+    gated = mode == "gated"
+    _require(gated or mode == "state_space", "mode is 'gated' or 'state_space'")
+    if gated:
+        _require(decay_logits is not None and decay_logits.dtype == torch.float32 and decay_logits.dim() == 2
+                 and decay_logits.stride(1) == 1 and decay_logits.shape == (T, heads * key_dim), "decay logits: float32 [T, heads * key_dim]")
+        _f32_vector(decay_bias, heads * key_dim, "the decay bias")
+        _require(decay_bias is not None, "the gated mode needs a decay bias")
+    else:
+        _require(dt is not None and dt.dim() == 2 and dt.stride(1) == 1 and dt.shape[0] == T and dt.shape[1] >= heads
+                 and dt.dtype == v.dtype, "dt must be [T, heads] of the model's type")
+        for vector in (dt_bias, a_log, skip):
+            _require(vector is not None, "the state-space mode needs dt_bias, a_log and skip")
+            _f32_vector(vector, heads, "a per-head constant")
+    out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=v.device)
+    _check(library().zb_decayed_state_scan(
+        _ptr(out), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(decay_logits),
+        decay_logits.stride(0) if gated else 0, _ptr(decay_bias), _ptr(dt), dt.stride(0) if not gated else 0,
+        _ptr(dt_bias), _ptr(a_log), _ptr(skip), 0, _ptr(state), state.stride(0), _ptr(slots), _ptr(row_q_start),
+        _ptr(row_q_len), slots.numel(), heads, key_dim, value_dim, int(heads_per_group), state.shape[0],
+        int(write_state), float(q_scale), float(inv_tau), 0 if gated else 1, DTYPE_CODE[v.dtype], _ptr(status),
+        _stream()), "decayed_state_scan")
+    return out
+
+
+def gated_group_rms_norm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group: int, eps: float,
+                         gate_first: bool) -> torch.Tensor:
+    """RMS norm of a float32 [T, W] over groups of ``group`` columns with a SiLU gate ([T, >= W], rows may
+    be strided) multiplied in before the norm (``gate_first``) or after it; ``w`` float32, used
+    periodically (W values, or one group's).  The result has the gate's type."""
+    _cuda(o, gate, w)
+    _require(o.dim() == 2 and o.is_contiguous() and o.dtype == torch.float32, "o must be a contiguous float32 [T, W]")
+    T, W = o.shape
+    _require(gate.dim() == 2 and gate.stride(1) == 1 and gate.shape[0] == T and gate.shape[1] >= W
+             and gate.dtype in DTYPE_CODE, "the gate must be [T, W] with unit inner stride")
+    _require(w.dtype == torch.float32 and w.is_contiguous() and w.numel() in (W, group), "w: float32, W or group values")
+    out = torch.empty((T, W), dtype=gate.dtype, device=o.device)
+    _check(library().zb_gated_group_rms_norm(_ptr(out), _ptr(o), _ptr(gate), gate.stride(0), _ptr(w), 0, w.numel(), T, W,
+                                             int(group), float(eps), int(gate_first), DTYPE_CODE[gate.dtype],
+                                             _stream()), "gated_group_rms_norm")
+    return out
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float,
+               out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """scale_a * a + scale_b * b in float32 with one rounding; a and b may be float32 whatever the result is."""
+    _cuda(a, b)
+    _require(a.shape == b.shape and a.dtype == b.dtype and a.dtype in DTYPE_CODE and a.is_contiguous()
+             and b.is_contiguous(), "two contiguous tensors of one shape and type")
+    out = torch.empty(a.shape, dtype=out_dtype or a.dtype, device=a.device)
+    _check(library().zb_scaled_sum(_ptr(out), _ptr(a), _ptr(b), float(scale_a), float(scale_b), a.numel(),
+                                   DTYPE_CODE[a.dtype], DTYPE_CODE[out.dtype], _stream()), "scaled_sum")
+    return out
+
+
 # ------------------------------------------------------------------ position and cache
 def kv_swizzle(pos: int, chunks: int) -> int:
     """By how much the 16-byte chunks of the cache row at position ``pos`` are permuted: logical chunk
@@ -434,29 +610,79 @@ def attention_tile_tokens(group: int) -> int:
     return library().zb_attention_simt_tile_tokens(int(group))
 
 
+def _cache_geometry(kv_cache: torch.Tensor, nkv: int, kd: int, vd: int, dtype: torch.dtype) -> tuple[int, int]:
+    """(pages, page size) of a cache whose pages hold [nkv][page][kd] keys and then [nkv][page][vd] values:
+    the five-dimensional form for equal widths, or flat pages."""
+    _require(kv_cache.is_contiguous() and kv_cache.dtype == dtype, "a cache must be contiguous and of the model's type")
+    if kv_cache.dim() == 5:
+        _require(kd == vd, "a [pages, 2, kv_heads, page_size, head_dim] cache has one width")
+        return _check_cache(kv_cache, nkv, kd, dtype)
+    _require(kv_cache.dim() == 2 and kv_cache.shape[1] % (nkv * (kd + vd)) == 0,
+             "a cache of two widths must be [pages, kv_heads * page_size * (key_dim + value_dim)]")
+    page_size = kv_cache.shape[1] // (nkv * (kd + vd))
+    _require(page_size * kv_cache.element_size() % 16 == 0, "a page must hold a multiple of 16 bytes per element column")
+    return kv_cache.shape[0], page_size
+
+
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
                     tile_q0: torch.Tensor, tile_tokens: int, row_q_start: torch.Tensor, row_q_len: torch.Tensor,
                     row_ctx: torch.Tensor, nh: int, nkv: int, hd: int, window: int, scale: float,
                     status: torch.Tensor, out: torch.Tensor | None = None,
-                    head_slopes: torch.Tensor | None = None) -> torch.Tensor:
+                    head_slopes: torch.Tensor | None = None, value_dim: int | None = None, chunk: int = 0,
+                    sinks: torch.Tensor | None = None) -> torch.Tensor:
     """The general kernel: causal attention of every new token over its request's pages.
     ``head_slopes`` (float32 [nh]): query head h adds head_slopes[h] * (key position - query position)
-    to its scores, a position encoding that is a bias on the scores."""
-    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes)
-    _require(head_slopes is None or (head_slopes.dtype == torch.float32 and head_slopes.is_contiguous()
-                                     and head_slopes.numel() == nh), "one float32 slope per query head")
+    to its scores, a position encoding that is a bias on the scores.  ``value_dim``: the width of the
+    values where it differs from the keys' ``hd``.  ``chunk`` > 0: a query sees only the keys of its own
+    run of ``chunk`` positions, runs counted from position 0.  ``sinks`` (float32 [nh]): exp(sinks[h])
+    joins the denominator of head h's softmax."""
+    _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes, sinks)
+    for per_head in (head_slopes, sinks):
+        _require(per_head is None or (per_head.dtype == torch.float32 and per_head.is_contiguous()
+                                      and per_head.numel() == nh), "one float32 value per query head")
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
+    vd = hd if value_dim is None else int(value_dim)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype in DTYPE_CODE, "q shape")
-    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    pages, page_size = _cache_geometry(kv_cache, nkv, hd, vd, q.dtype)
     if out is None:
-        out = torch.empty_like(q)
-    _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
+        out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
+    _require(out.shape == (q.shape[0], nh * vd) and out.dtype == q.dtype and out.is_contiguous(), "out must be [T, heads * value_dim]")
     _check(library().zb_paged_attention_simt(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), int(tile_tokens), _ptr(row_q_start),
-        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), _ptr(head_slopes), DTYPE_CODE[q.dtype],
-        _ptr(status), _stream()), "paged_attention")
+        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, vd, int(window), int(chunk), float(scale), _ptr(head_slopes),
+        _ptr(sinks), DTYPE_CODE[q.dtype], _ptr(status), _stream()), "paged_attention")
     return out
+
+
+def qkv_pairs(qkv: torch.Tensor, nh: int, nkv: int, kd: int, vd: int, bias: torch.Tensor | None,
+              q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, eps: float, freqs: torch.Tensor | None,
+              rot_dims: int, positions: torch.Tensor, token_row: torch.Tensor, kv_cache: torch.Tensor | None,
+              block_table: torch.Tensor, status: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Bias, per-head RMS norm of q and k, rotation of adjacent pairs by position * freqs on the first
+    ``rot_dims`` dimensions, and the cache write of k and v (keys ``kd`` wide, values ``vd``); returns the
+    queries [T, nh * kd] in ``dtype``.  ``qkv`` may be float32 whatever ``dtype`` is; bias, norm scales and
+    frequencies are float32.  Without ``kv_cache`` only the queries are made."""
+    _cuda(qkv, bias, q_norm_w, k_norm_w, freqs, positions, token_row, kv_cache, block_table, status)
+    _i32(positions, token_row, block_table)
+    T = qkv.shape[0]
+    width = nh * kd + (nkv * (kd + vd) if kv_cache is not None else 0)
+    _require(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1 and qkv.dtype in DTYPE_CODE,
+             "qkv must be [T, heads*key_dim + kv_heads*(key_dim + value_dim)] with unit inner stride")
+    for vector, size in ((bias, width), (q_norm_w, kd), (k_norm_w, kd), (freqs, rot_dims // 2)):
+        _require(vector is None or (vector.dtype == torch.float32 and vector.is_contiguous() and vector.numel() == size),
+                 f"a float32 vector of {size} values")
+    _require(positions.numel() == T and token_row.numel() == T and block_table.dim() == 2, "one position and row per token")
+    pages, page_size = (0, 1)
+    if kv_cache is not None:
+        pages, page_size = _cache_geometry(kv_cache, nkv, kd, vd, dtype)
+    q_out = torch.empty((T, nh * kd), dtype=dtype, device=qkv.device)
+    _check(library().zb_qkv_pairs(
+        _ptr(q_out), _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(freqs),
+        int(rot_dims), _ptr(positions), _ptr(token_row), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
+        page_size, pages, block_table.shape[0], T, nh, nkv, kd, vd, DTYPE_CODE[qkv.dtype], DTYPE_CODE[dtype],
+        _ptr(status), _stream()), "qkv_pairs")
+    return q_out
 
 
 def paged_decode_supported(nh: int, nkv: int, hd: int, dtype: torch.dtype) -> bool:

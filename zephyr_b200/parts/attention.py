@@ -9,6 +9,15 @@ The three projections run as one product over the row-concatenated weight.  Per-
 and the cache write are one kernel when the position encoding offers rotation tables
 (``PositionEncoding.as_rotation_tables``: the NeoX rotation, or no encoding at all); any other
 encoding goes through its own ``apply`` and separate norm and write kernels.
+
+Beyond that form the part takes, as parameters: biases on the four projections (``q_bias`` ...), values
+of another width than the keys (``value_dim``), a score scale of its own (``scale``), a chunked mask
+(``chunk`` = n: position i sees j <= i only if i // n == j // n, chunks counted from position 0), a
+learned sink per query head (``sinks``: exp(sink_h) joins the softmax's denominator, with no key, no
+value and no scaling), and the rotation of adjacent pairs on part of the head (position kind
+``rope_pairs``).  Any of these sends the layer down the general path: the projection's float32 output
+goes through one kernel (bias, norms, rotation, cache write: ``ops.qkv_pairs``) and the general
+attention kernel, which takes all of them, for prompts and single tokens alike.
 """
 
 from __future__ import annotations
@@ -22,7 +31,7 @@ from ..cache import PagedCacheSpec
 from ..config.errors import ConfigError
 from ..config.spec import LayerCall, MixerSpec
 from ..kernels import ops
-from ..weights.loader import ROLE_LINEAR, ROLE_NORM, WeightDecl
+from ..weights.loader import ROLE_LINEAR, ROLE_NORM, ROLE_ZERO, WeightDecl
 from .base import POSITION_ENCODINGS, Mixer, StepContext, lookup, register_mixer
 
 
@@ -41,9 +50,13 @@ class Attention(Mixer):
         self.dtype = dtype
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv != 0:
             raise ConfigError("attention needs positive head counts with heads divisible by kv_heads")
-        if self.hd % 16 != 0 or not 16 <= self.hd <= 256:
-            raise ConfigError(f"attention kernels take head sizes 16..256 in steps of 16, not {self.hd}")
-        self.scale = 1.0 / math.sqrt(float(self.hd))
+        if self.hd <= 0 or self.hd > 256:
+            raise ConfigError(f"attention kernels take head sizes up to 256, not {self.hd}")
+        self.vd = int(p.get("value_dim") or self.hd)
+        self.chunk = int(p.get("chunk") or 0)
+        if self.vd <= 0 or self.vd > 256 or self.chunk < 0:
+            raise ConfigError("attention takes value widths up to 256 and a chunk size that is not negative")
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
         self.w_qkv = torch.cat([weights[p["q_proj"]], weights[p["k_proj"]], weights[p["v_proj"]]], dim=0).contiguous()
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = weights[p["o_proj"]]
@@ -56,6 +69,22 @@ class Attention(Mixer):
                 spec.position, dtype, device)
         else:
             self.position = None
+        biases = [weights[p[name]] if p.get(name) else None for name in ("q_bias", "k_bias", "v_bias")]
+        if any(b is not None for b in biases) and any(b is None for b in biases):
+            raise ConfigError("q, k and v biases come together")
+        self.qkv_bias = torch.cat([b.float() for b in biases]).contiguous() if biases[0] is not None else None
+        self.o_bias = weights[p["o_bias"]].float().contiguous() if p.get("o_bias") else None
+        self.sinks = weights[p["sinks"]].float().contiguous() if p.get("sinks") else None
+        pairs = getattr(self.position, "as_pair_frequencies", None)
+        self.pair_freqs, self.pair_dims = pairs() if pairs is not None else (None, 0)
+        # What only the general path takes.
+        self.general = (pairs is not None or self.vd != self.hd or self.chunk > 0 or self.sinks is not None
+                        or self.qkv_bias is not None or self.o_bias is not None or p.get("scale") is not None)
+        if self.general:
+            self._init_general(p)
+            return
+        if self.hd % 16 != 0 or self.hd < 16:
+            raise ConfigError(f"attention kernels take head sizes 16..256 in steps of 16, not {self.hd}")
         # The fused kernels (norm + rotation + cache write, and the decode attention that does all of it
         # itself) rotate NeoX pairs by per-position angles from float32 tables; an encoding says whether
         # it is one of those, and any other goes through its own ``apply``.
@@ -75,19 +104,41 @@ class Attention(Mixer):
         self.fast_prefill = self.score_slopes is None and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
+    def _init_general(self, p) -> None:
+        if self.hd % 2 != 0:
+            raise ConfigError("the general attention path takes even key widths")
+        if self.score_slopes_wanted():
+            raise ConfigError("a bias on the scores and the general path's extras do not combine")
+        if self.position is not None and self.pair_freqs is None and self.position.as_rotation_tables() != (None, None):
+            raise ConfigError("the general attention path rotates adjacent pairs or nothing")
+        self.q_norm = self.q_norm.float().contiguous() if self.q_norm is not None else None
+        self.k_norm = self.k_norm.float().contiguous() if self.k_norm is not None else None
+        self.score_slopes = None
+        self.group = self.nh // self.nkv
+        self.tile_tokens = ops.attention_tile_tokens(self.group)
+        self.fast_decode = self.fast_prefill = self.fused_position = False
+
+    def score_slopes_wanted(self) -> bool:
+        return self.position is not None and self.position.as_score_slopes() is not None
+
     @staticmethod
     def weight_decls(spec: MixerSpec) -> dict[str, WeightDecl]:
         p = spec.params
         hidden, nh, nkv, hd = int(p["hidden_size"]), int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        vd = int(p.get("value_dim") or hd)
         decls = {
             p["q_proj"]: WeightDecl((nh * hd, hidden), ROLE_LINEAR),
             p["k_proj"]: WeightDecl((nkv * hd, hidden), ROLE_LINEAR),
-            p["v_proj"]: WeightDecl((nkv * hd, hidden), ROLE_LINEAR),
-            p["o_proj"]: WeightDecl((hidden, nh * hd), ROLE_LINEAR),
+            p["v_proj"]: WeightDecl((nkv * vd, hidden), ROLE_LINEAR),
+            p["o_proj"]: WeightDecl((hidden, nh * vd), ROLE_LINEAR),
         }
         if p.get("q_norm"):
             decls[p["q_norm"]] = WeightDecl((hd,), ROLE_NORM)
             decls[p["k_norm"]] = WeightDecl((hd,), ROLE_NORM)
+        for name, size in (("q_bias", nh * hd), ("k_bias", nkv * hd), ("v_bias", nkv * vd), ("o_bias", hidden),
+                           ("sinks", nh)):
+            if p.get(name):
+                decls[p[name]] = WeightDecl((size,), ROLE_ZERO)
         return decls
 
     def weights_read(self) -> list[torch.Tensor]:
@@ -96,8 +147,9 @@ class Attention(Mixer):
     @staticmethod
     def cache_spec(spec: MixerSpec) -> PagedCacheSpec:
         p = spec.params
-        return PagedCacheSpec(int(p["num_kv_heads"]), key_dim=int(p["head_dim"]), value_dim=int(p["head_dim"]),
-                              window=int(p.get("window", 0)))
+        return PagedCacheSpec(int(p["num_kv_heads"]), key_dim=int(p["head_dim"]),
+                              value_dim=int(p.get("value_dim") or p["head_dim"]), window=int(p.get("window", 0)),
+                              chunk=int(p.get("chunk") or 0))
 
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
@@ -171,14 +223,42 @@ class Attention(Mixer):
                                 ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes)
         return out
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall) -> torch.Tensor:
+    takes_out_dtype = True
+
+    def _forward_general(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
+                         out_dtype: torch.dtype | None) -> torch.Tensor:
+        """Projection in float32 -> bias, norms, rotation, cache write -> the general kernel -> output
+        projection (its bias added to the float32 or rounded product as ``out_dtype`` says)."""
+        table = ctx.block_table(call.cache)
+        # A layer that reads another layer's cache needs no k and v.
+        weight, bias, cache = self.w_qkv, self.qkv_bias, ctx.caches[call.cache]
+        if not call.writes_cache:
+            weight, cache = self.w_q, None
+            bias = bias[: self.nh * self.hd] if bias is not None else None
+        projected = ops.linear(x, weight, out_dtype=torch.float32)
+        q = ops.qkv_pairs(projected, self.nh, self.nkv, self.hd, self.vd, bias, self.q_norm, self.k_norm, self.eps,
+                          self.pair_freqs, self.pair_dims, ctx.positions, ctx.token_row, cache, table, ctx.status,
+                          self.dtype)
+        tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
+        attended = ops.paged_attention(q, ctx.caches[call.cache], table, tile_row, tile_q0, self.tile_tokens,
+                                       ctx.row_q_start, ctx.row_q_len, ctx.row_ctx, self.nh, self.nkv, self.hd,
+                                       self.window, self.scale, ctx.status, value_dim=self.vd, chunk=self.chunk,
+                                       sinks=self.sinks)
+        return ops.linear(attended, self.w_o, out_dtype=out_dtype, bias=self.o_bias)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
+                out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        if self.general:
+            return self._forward_general(x, ctx, call, out_dtype)
+        if out_dtype not in (None, x.dtype):
+            return self.forward(x, ctx, call).to(out_dtype)
         if self.fused_position and call.writes_cache:
             return ops.linear(self.core(ops.linear(x, self.w_qkv), ctx, call), self.w_o)
         q = self._project_and_store(x, ctx, call)
         return ops.linear(self.attend(q, ctx, call), self.w_o)
 
     def projections(self, call: LayerCall) -> tuple[torch.Tensor, torch.Tensor] | None:
-        if not self.fused_position:
+        if not self.fused_position or self.general:
             return None
         return (self.w_qkv if call.writes_cache else self.w_q), self.w_o
 

@@ -121,12 +121,17 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if ``forward`` takes ``out_dtype=`` and can hand out its result in float32 (the float32 sums
+    # of its last product, before any rounding): a mixer that adds up several mixers asks for that.
+    takes_out_dtype = False
+
     def __init__(self, spec: MixerSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype,
                  device: torch.device | str): ...
 
     @staticmethod
-    def cache_spec(spec: MixerSpec) -> PagedCacheSpec | StateCacheSpec | None:
-        """What this mixer stores per request: pages, a fixed state, or nothing."""
+    def cache_spec(spec: MixerSpec) -> PagedCacheSpec | StateCacheSpec | None | tuple:
+        """What this mixer stores per request: pages, a fixed state, or nothing; a tuple of those for a
+        mixer that keeps several stores (its call then names one cache id for each, ``LayerCall.caches``)."""
         return None
 
     @staticmethod
@@ -163,17 +168,40 @@ class FeedForward(Part):
 
 
 @dataclass
+class DeferredSum:
+    """hidden += mult * norm(delta), not yet done: the consumer of the stream either does it in the
+    same pass as its own norm (``Norm.add_scaled`` of norms that have it) or lets ``apply`` do it."""
+
+    delta: torch.Tensor
+    norm: "Norm"
+    mult: float
+
+    def apply(self, hidden: torch.Tensor, then: "Norm | None" = None) -> torch.Tensor | None:
+        """Do the sum in place; with ``then`` return then(hidden) as well."""
+        fused = getattr(self.norm, "add_scaled", None)
+        if fused is not None and hidden.dtype == torch.float32 and (then is None or type(then) is type(self.norm)):
+            return fused(hidden, self.delta, self.mult, then)
+        hidden.add_(self.norm.forward(self.delta).to(hidden.dtype), alpha=self.mult)
+        return then.forward(hidden) if then is not None else None
+
+
+@dataclass
 class ResidualStream:
     """The hidden states between blocks: the stream itself and a summand not yet added, which the
-    next norm adds in the same pass that normalises."""
+    next norm adds in the same pass that normalises (``pending``: added as it is; ``deferred``: normed
+    and scaled first)."""
 
     hidden: torch.Tensor
     pending: torch.Tensor | None = None
+    deferred: DeferredSum | None = None
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
             self.hidden.add_(self.pending)
             self.pending = None
+        if self.deferred is not None:
+            self.deferred.apply(self.hidden)
+            self.deferred = None
         return self.hidden
 
 

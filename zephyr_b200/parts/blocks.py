@@ -3,14 +3,22 @@
 ``prenorm_residual``: r = x + mixer(norm1(x)); x' = r + ffn(norm2(r)), the sums in float32
 (reference: src/model/causal_lm/qwen3.cpp:79-88).  Each sum is folded into the norm that follows
 it, so the block hands its last summand on as ``pending``.
+
+``sandwich_residual``: a norm before and one behind each part, and a multiplier m on what joins the
+stream: r = x + m * mixer_out(mixer(mixer_norm(x))); x' = r + m * ffn_out(ffn(ffn_norm(r))).  The
+stream is float32.  The feed-forward may be missing; the layer is then its first half.  Each sum
+runs in the same kernel as the norm that follows it where the norms offer that (``Norm.add_scaled``),
+the last one as a ``DeferredSum`` that the next block or the output part takes up.
 """
 
 from __future__ import annotations
 
 from typing import Mapping
 
+import torch
+
 from ..config.spec import LayerCall
-from .base import Block, FeedForward, Mixer, Norm, ResidualStream, StepContext, register_block
+from .base import Block, DeferredSum, FeedForward, Mixer, Norm, ResidualStream, StepContext, register_block
 from .fused import BlockPlan
 
 
@@ -45,4 +53,35 @@ class PreNormResidual(Block):
         return BlockPlan(self.mixer, mixer_norm, ffn_norm, gated[0], gated[1])
 
 
+class SandwichResidual(Block):
+    graph_safe = True
+    feed_forward_optional = True
+
+    norm_names = ("mixer", "mixer_out", "feed_forward", "feed_forward_out")
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norms: Mapping[str, Norm], params=None):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+        self.mult = float((params or {}).get("residual_mult", 1.0))
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
+        if stream.pending is not None or stream.hidden.dtype != torch.float32:
+            stream.hidden = stream.flush().float()
+        norms, hidden = self.norms, stream.hidden
+        if stream.deferred is not None:
+            normed = stream.deferred.apply(hidden, then=norms["mixer"])
+            stream.deferred = None
+        else:
+            normed = norms["mixer"].forward(hidden)
+        mixed = self.mixer.forward(normed, ctx, call)
+        summand = DeferredSum(mixed, norms["mixer_out"], self.mult)
+        if self.feed_forward is not None:
+            normed = summand.apply(hidden, then=norms["feed_forward"])
+            summand = DeferredSum(self.feed_forward.forward(normed), norms["feed_forward_out"], self.mult)
+        stream.deferred = summand
+        return stream
+
+
 register_block("prenorm_residual", PreNormResidual)
+register_block("sandwich_residual", SandwichResidual)

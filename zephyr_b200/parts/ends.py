@@ -27,6 +27,8 @@ class Embedding(InputPart):
 
     def __init__(self, spec: InputSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype):
         self.table = weights[spec.params["weight"]]
+        # A model whose residual stream is float32 takes the table's rows as float32 from the start.
+        self.float32_stream = bool(spec.params.get("float32_stream", False))
 
     @staticmethod
     def weight_decls(spec: InputSpec) -> dict[str, WeightDecl]:
@@ -37,6 +39,8 @@ class Embedding(InputPart):
         return []          # a step gathers a few rows of the table; it does not stream it
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.float32_stream:
+            return ops.embedding_f32(self.table, ctx.token_ids, ctx.status)
         return ops.embedding(self.table, ctx.token_ids, ctx.status)
 
 
@@ -64,6 +68,8 @@ class NormHead(OutputPart):
         wanted = ctx.logit_tokens
         if wanted.numel() == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=stream.hidden.device)
+        if stream.deferred is not None:
+            stream.flush()
         rows = ops.gather_rows(stream.hidden, wanted, ctx.status)
         if stream.pending is not None:
             normed = self.norm.add_forward(rows, ops.gather_rows(stream.pending, wanted, ctx.status))

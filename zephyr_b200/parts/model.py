@@ -23,10 +23,14 @@ from .fused import DecodeChains
 def _layer_classes(layer: LayerSpec):
     block = lookup(BLOCKS, "block", layer.block)
     wanted, given = set(getattr(block, "norm_names", ())), set(layer.norms)
+    if layer.feed_forward is None:          # a layer that is only its first half brings only that half's norms
+        wanted = {name for name in wanted if not name.startswith("feed_forward")}
     if wanted and wanted != given:
         raise ConfigError(f"block '{layer.block}' places the norms {sorted(wanted)}, the layer brings {sorted(given)}")
+    if layer.feed_forward is None and not getattr(block, "feed_forward_optional", False):
+        raise ConfigError(f"block '{layer.block}' needs a feed-forward")
     return (block, lookup(MIXERS, "mixer", layer.mixer.kind),
-            lookup(FEED_FORWARDS, "feed-forward", layer.feed_forward.kind),
+            lookup(FEED_FORWARDS, "feed-forward", layer.feed_forward.kind) if layer.feed_forward is not None else None,
             {name: lookup(NORMS, "norm", norm.kind) for name, norm in layer.norms.items()})
 
 
@@ -47,7 +51,8 @@ def expected_weights(spec: ModelSpec) -> dict[str, WeightDecl]:
     for layer in spec.layers:
         _, mixer, ffn, norms = _layer_classes(layer)
         merge(mixer.weight_decls(layer.mixer))
-        merge(ffn.weight_decls(layer.feed_forward))
+        if ffn is not None:
+            merge(ffn.weight_decls(layer.feed_forward))
         for name, norm in norms.items():
             merge(norm.weight_decls(layer.norms[name]))
     merge(lookup(OUTPUTS, "output part", spec.output.kind).weight_decls(spec.output))
@@ -60,12 +65,29 @@ def cache_specs(spec: ModelSpec) -> list[PagedCacheSpec | StateCacheSpec | None]
     for call in spec.run_order:
         layer = spec.layers[call.layer]
         mixer = lookup(MIXERS, "mixer", layer.mixer.kind)
-        need = mixer.cache_spec(layer.mixer)
-        if call.writes_cache:
-            out[call.cache] = need
-        elif out[call.cache] != need:
-            raise ConfigError(f"layer {call.layer} reads cache {call.cache}, whose shape does not fit its mixer")
+        needs = mixer.cache_spec(layer.mixer)
+        if not isinstance(needs, tuple):
+            needs = (needs,)
+        if len(needs) != len(call.caches):
+            raise ConfigError(f"the mixer of layer {call.layer} keeps {len(needs)} stores, its call names {len(call.caches)}")
+        for cache, need in zip(call.caches, needs):
+            if call.writes_cache:
+                out[cache] = need
+            elif out[cache] != need:
+                raise ConfigError(f"layer {call.layer} reads cache {cache}, whose shape does not fit its mixer")
     return out
+
+
+def run_order_for(layers) -> tuple:
+    """Every layer once, in order, each with stores of its own: as many cache ids as its mixer keeps stores."""
+    from ..config.spec import LayerCall
+    calls, next_id = [], 0
+    for index, layer in enumerate(layers):
+        needs = lookup(MIXERS, "mixer", layer.mixer.kind).cache_spec(layer.mixer)
+        count = len(needs) if isinstance(needs, tuple) else 1
+        calls.append(LayerCall(layer=index, cache=next_id, extra_caches=tuple(range(next_id + 1, next_id + count))))
+        next_id += count
+    return tuple(calls)
 
 
 def tile_requests(spec: ModelSpec) -> list[tuple[int, str]]:
@@ -89,13 +111,16 @@ class Model:
         self.layers = []
         for layer in spec.layers:
             block, mixer, ffn, norms = _layer_classes(layer)
-            self.layers.append(block(mixer(layer.mixer, weights, dtype, device), ffn(layer.feed_forward, weights, dtype),
-                                     {name: cls(layer.norms[name], weights, dtype) for name, cls in norms.items()}))
+            extra = {"params": layer.block_params} if layer.block_params else {}
+            self.layers.append(block(mixer(layer.mixer, weights, dtype, device),
+                                     ffn(layer.feed_forward, weights, dtype) if ffn is not None else None,
+                                     {name: cls(layer.norms[name], weights, dtype) for name, cls in norms.items()},
+                                     **extra))
         self.cache_specs = cache_specs(spec)
         parts = [self.input, self.output]
         for block in self.layers:
             parts += [block, block.mixer, block.feed_forward, *getattr(block, "norms", {}).values(),
-                      getattr(block.mixer, "position", None)]
+                      getattr(block.mixer, "position", None), *getattr(block.mixer, "branches", ())]
         self.graph_safe = all(getattr(part, "graph_safe", False) for part in parts if part is not None)
         self.tile_requests = tile_requests(spec)
         # Steps of a few tokens run as fused chains of products where every block offers its pieces.
@@ -136,7 +161,7 @@ class Model:
         for call in self.spec.run_order:
             block = self.layers[call.layer]
             for part in (block.mixer, block.feed_forward, *getattr(block, "norms", {}).values()):
-                for tensor in part.weights_read():
+                for tensor in (part.weights_read() if part is not None else ()):
                     add(tensor)
         # Tensors that share a storage overlap (a matrix and a view of its first rows): such a storage
         # counts once, and never for more than it holds.

@@ -1,6 +1,8 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, statistics in float32, the scale multiplied after
 the normalisation and not as (1 + w) (reference: src/layer/normalization.cpp:10-18,
-deps/ttl/src/kernels/normalization/normalization.cu:76-139)."""
+deps/ttl/src/kernels/normalization/normalization.cu:76-139).
+
+LayerNorm: mean and variance of the row, scale and shift."""
 
 from __future__ import annotations
 
@@ -10,7 +12,8 @@ import torch
 
 from ..config.spec import NormSpec
 from ..kernels import ops
-from ..weights.loader import ROLE_NORM, WeightDecl
+from ..config.errors import ConfigError
+from ..weights.loader import ROLE_NORM, ROLE_ZERO, WeightDecl
 from .base import Norm, register_norm
 
 
@@ -36,4 +39,38 @@ class RMSNorm(Norm):
         return self.weight, self.eps
 
 
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b, the variance being the mean of the squared deviations;
+    statistics, scale and shift in float32.  The input may be a float32 residual stream or a tensor of
+    the model's type; the output has the model's type.  ``add_scaled`` is the fused form a block with
+    norms behind its parts uses: residual += m * this_norm(delta), then the next norm of the sum."""
+
+    graph_safe = True
+
+    def __init__(self, spec: NormSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype):
+        self.size = spec.size
+        self.eps = float(spec.eps)
+        self.dtype = dtype
+        self.weight = weights[spec.weight].float().contiguous()
+        self.bias = weights[spec.bias].float().contiguous()
+
+    @staticmethod
+    def weight_decls(spec: NormSpec) -> dict[str, WeightDecl]:
+        if spec.bias is None:
+            raise ConfigError("a layer norm needs the name of its shift")
+        return {spec.weight: WeightDecl((spec.size,), ROLE_NORM), spec.bias: WeightDecl((spec.size,), ROLE_ZERO)}
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.layer_norm(x, self.weight, self.bias, self.eps, out_dtype=self.dtype)
+
+    def add_scaled(self, residual: torch.Tensor, delta: torch.Tensor, mult: float,
+                   then: "LayerNorm | None" = None) -> torch.Tensor | None:
+        """residual (float32) += mult * norm(delta), in place; with ``then`` also returns then(residual)."""
+        if then is None:
+            return ops.residual_layer_norm(residual, delta, self.weight, self.bias, self.eps, mult)
+        return ops.residual_layer_norm(residual, delta, self.weight, self.bias, self.eps, mult,
+                                       then.weight, then.bias, then.eps)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

@@ -32,10 +32,23 @@ ROLE_EMBEDDING = "embedding"  # N(0, 0.02)
 _ROLE_INIT = {ROLE_LINEAR: (0.0, 0.02), ROLE_NORM: (1.0, 0.01), ROLE_EMBEDDING: (0.0, 0.02)}
 
 
+ROLE_ZERO = "zero"            # N(0, 0.02) as well: biases and other shifts around zero
+
+_ROLE_INIT[ROLE_ZERO] = (0.0, 0.02)
+
+
 @dataclass(frozen=True)
 class WeightDecl:
+    """``shape`` may hold -1 for a size that only the checkpoint gives (an inner rank no configuration
+    key names): any size fits there, and the part reads it from the tensor.  Such a declaration cannot
+    be filled with random values."""
+
     shape: tuple[int, ...]
     role: str = ROLE_LINEAR
+
+
+def shape_fits(found: tuple[int, ...], declared: tuple[int, ...]) -> bool:
+    return len(found) == len(declared) and all(d in (-1, f) for f, d in zip(found, declared))
 
 
 class WeightStore(Protocol):
@@ -51,7 +64,7 @@ def check_store(store: WeightStore, expected: Mapping[str, WeightDecl], ignorabl
     missing = sorted(name for name in expected if name not in present)
     unexpected = sorted(name for name in present if name not in expected and name not in ignorable)
     wrong = sorted((name, tuple(store.shape(name)), tuple(decl.shape)) for name, decl in expected.items()
-                   if name in present and tuple(store.shape(name)) != tuple(decl.shape))
+                   if name in present and not shape_fits(tuple(store.shape(name)), tuple(decl.shape)))
     not_float = sorted(name for name, decl in expected.items()
                        if name in present and not store.dtype(name).is_floating_point)
     if not (missing or unexpected or wrong or not_float):
@@ -113,6 +126,8 @@ def random_tensor(seed: int, name: str, decl: WeightDecl, dtype: torch.dtype,
     and they are rounded.  The two give different streams: a model folder holds whatever made it."""
     if decl.role not in _ROLE_INIT:
         raise WeightError(f"tensor '{name}' has the unknown role {decl.role!r}")
+    if any(size < 0 for size in decl.shape):
+        raise WeightError(f"tensor '{name}' has a size that only a checkpoint gives; random values need it spelled out")
     mean, std = _ROLE_INIT[decl.role]
     if torch.device(device).type == "cuda" and dtype in (torch.bfloat16, torch.float32):
         from ..kernels import ops
