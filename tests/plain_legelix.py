@@ -91,6 +91,33 @@ def plain_rotate(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, 
 
 
 # ----------------------------------------------------------------------------- chunked attention with a sink
+def plain_attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, size: int | None,
+                         sinks: torch.Tensor | None, start: int = 0) -> torch.Tensor:
+    """q [T, H, D] at positions start..start+T-1 over k [start+T, G, D], v [start+T, G, V]: causal, only
+    within a position's own chunk of ``size`` (chunks counted from position 0), softmax with one more
+    term exp(sink_h) in the denominator that has no key and no value.  Returns [T, H, V]."""
+    T, H, _ = q.shape
+    G, V = k.shape[1], v.shape[2]
+    out = torch.zeros(T, H, V, dtype=F64)
+    i = torch.arange(start, start + T)[:, None]
+    j = torch.arange(k.shape[0])[None, :]
+    seen = j <= i
+    if size:
+        seen = seen & ((i // size) == (j // size))
+    for head in range(H):
+        g = head // (H // G)
+        score = ((q[:, head] @ k[:, g].T) * scale).masked_fill(~seen, float("-inf"))
+        top = score.max(dim=-1, keepdim=True).values
+        if sinks is not None:
+            top = torch.maximum(top, sinks[head])
+        e = torch.exp(score - top)
+        denominator = e.sum(dim=-1, keepdim=True)
+        if sinks is not None:
+            denominator = denominator + torch.exp(sinks[head] - top)
+        out[:, head] = (e / denominator) @ v[:, g]
+    return out
+
+
 def plain_chunked_sink_attention(h: torch.Tensor, W: dict, p: dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, D, V = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
@@ -106,19 +133,7 @@ def plain_chunked_sink_attention(h: torch.Tensor, W: dict, p: dict, eps: float) 
         q = plain_rotate(q, positions, freqs, rot["dims"])
         k = plain_rotate(k, positions, freqs, rot["dims"])
     size = p["mask"]["size"] if p.get("mask") else None
-    out = torch.zeros(T, H, V, dtype=F64)
-    for head in range(H):
-        g = head // (H // G)
-        score = (q[:, head] @ k[:, g].T) * float(p["scale"])
-        i, j = positions[:, None], positions[None, :]
-        seen = j <= i
-        if size:
-            seen = seen & ((i // size) == (j // size))
-        score = score.masked_fill(~seen, float("-inf"))
-        top = torch.maximum(score.max(dim=-1, keepdim=True).values, W["sink"][head])
-        e = torch.exp(score - top)
-        denominator = e.sum(dim=-1, keepdim=True) + torch.exp(W["sink"][head] - top)
-        out[:, head] = (e / denominator) @ v[:, g]
+    out = plain_attention_core(q, k, v, float(p["scale"]), size, W["sink"])
     return out.reshape(T, H * V) @ W["o"].T + W["o.b"]
 
 
