@@ -62,9 +62,17 @@ CONFIGS = {
         parallel(attention(4, 1, 16, 16, 0.25), mamba(1, 64, 32, 1, 2, 2), 1.0, 1.0, 160),
         parallel(attention(8, 2, 16, 48, 0.25, chunk=64, rot={"base": 100.0, "dims": 8}),
                  mamba(8, 16, 48, 4, 1, 4), 0.5, 2.0, None)]},
+    # S: keys and values of one width (32, then 64): in bfloat16 these layers take the split-context
+    # decode kernel and the tensor-core prompt kernel, which mask chunks and count sinks themselves
+    "S": {"architecture": "Legelix", "vocab": 80, "width": 64, "residual_mult": 0.5, "norm": {"eps": 1e-6}, "layers": [
+        parallel(attention(4, 2, 32, 32, 0.18, chunk=40, rot={"base": 300.0, "dims": 32, "scaling": SCALING}),
+                 mamba(2, 32, 16, 2, 4, 1), 1.2, 0.9, 96),
+        gla(1, 32, 64, 16.0, 96),
+        parallel(attention(2, 2, 64, 64, 0.125, chunk=72, rot={"base": 10000.0, "dims": 16}),
+                 mamba(2, 32, 16, 1, 4, 2), 0.7, 1.0, 96)]},
 }
-PAGE_SIZE = {"P": 16, "Q": 16, "R": 32}
-DECAY_RANK = {"P": 8, "Q": 5, "R": 16}
+PAGE_SIZE = {"P": 16, "Q": 16, "R": 32, "S": 16}
+DECAY_RANK = {"P": 8, "Q": 5, "R": 16, "S": 4}
 
 
 def make_weights(config: dict, rank: int, seed: int) -> dict[str, torch.Tensor]:

@@ -80,7 +80,8 @@ def assert_rows_match(rows, requests, folder, dtype, what):
         f"{what}: first wrong logits at request {over[0][0]} position {over[0][1]}: {ratios[over[0]]:.2f} bounds"
 
 
-LENGTHS = {"P": [70, 128, 45, 33, 100, 5, 17, 64], "Q": [1, 9, 33, 70, 41, 96, 23, 2], "R": [150, 40, 66, 129, 31, 200]}
+LENGTHS = {"P": [70, 128, 45, 33, 100, 5, 17, 64], "Q": [1, 9, 33, 70, 41, 96, 23, 2], "R": [150, 40, 66, 129, 31, 200],
+           "S": [170, 40, 81, 129, 31, 300, 72, 5]}
 TRACES = {"whole": trace_whole, "tail": functools.partial(trace_tail, tail=60),
           "portions": functools.partial(trace_portions, sizes=(1, 1, 2, 7, 2, 5, 3, 2, 11, 2, 4, 1, 6, 23)),
           "mixed": trace_mixed, "batched": trace_batched_tail}
@@ -124,7 +125,7 @@ def test_captured_steps_equal_launched_ones(folders, cuda_device):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_over_many_chunk_edges(folders, cuda_device, dtype):
     """A short prompt and 190 tokens decoded one by one: 19 chunk edges of Q, 7 of P."""
-    for name in ("Q", "P"):
+    for name in ("Q", "P", "S"):
         folder = folders(name, dtype)
         requests = {"long": random_tokens(CONFIGS[name]["vocab"], 200, seed=9)}
         steps = trace_tail(requests, tail=190)
@@ -333,7 +334,9 @@ def test_state_space_recurrence_convolution_and_gated_norm(cuda_device):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("kd,vd,heads,kv_heads,chunk,rot_dims,page", [(32, 16, 4, 2, 24, 16, 16), (24, 40, 3, 3, 10, 24, 16),
                                                                    (64, 64, 8, 1, 200, 32, 32), (18, 6, 2, 1, 0, 0, 16),
-                                                                   (32, 16, 4, 2, 24, 0, 16), (16, 48, 2, 2, 16, 0, 32)])
+                                                                   (32, 16, 4, 2, 24, 0, 16), (16, 48, 2, 2, 16, 0, 32),
+                                                                   (32, 32, 4, 2, 40, 0, 16), (128, 128, 4, 1, 100, 64, 16),
+                                                                   (96, 96, 6, 2, 33, 0, 32)])
 def test_chunked_sink_attention_at_its_edges(cuda_device, dtype, kd, vd, heads, kv_heads, chunk, rot_dims, page):
     """Queries that point at one key each: the key far back in the chunk, the first key of the chunk, and
     the last key of the chunk before (which must not be seen), in a prompt's portion and decoded
@@ -391,6 +394,19 @@ def test_chunked_sink_attention_at_its_edges(cuda_device, dtype, kd, vd, heads, 
         tile_q0 = torch.arange(0, n, tile, dtype=torch.int32, device=cuda_device)
         outs.append(ops.paged_attention(qs, cache, table, torch.zeros_like(tile_q0), tile_q0, tile, *rows, heads, kv_heads,
                                         kd, 0, scale, status, value_dim=vd, chunk=chunk, sinks=sinks.to(cuda_device)))
+        if kd == vd and ops.paged_decode_supported(heads, kv_heads, kd, torch_dtype):
+            # the same tokens through the kernels for prompts and for single tokens: they mask and count alike
+            paged = cache.view(blocks + 1, 2, kv_heads, page, kd)
+            fast = torch.full_like(outs[-1], float("nan"))
+            if n == 1:
+                ops.paged_decode(qs, paged, table, rows[0], rows[0], rows[2], at + 1, heads, kv_heads, kd, 0, scale,
+                                 status, fast, chunk=chunk, sinks=sinks.to(cuda_device))
+            else:
+                wide = ops.paged_prefill_tile_tokens()
+                wide_q0 = torch.arange(0, n, wide, dtype=torch.int32, device=cuda_device)
+                ops.paged_prefill(qs, paged, table, torch.zeros_like(wide_q0), wide_q0, *rows, heads, kv_heads, kd, 0,
+                                  scale, status, fast, chunk=chunk, sinks=sinks.to(cuda_device))
+            assert (fast.double() - outs[-1].double()).abs().max().item() < 0.03 * max(1.0, float(expected.abs().max())), (n, at)
         at += n
     ops.check_status(status)
     got = torch.cat(outs).cpu().double()

@@ -61,6 +61,8 @@ struct DecodeArgs {
   int* counters;                 // [n_rows, nkv] zero on entry, zero again on exit
   int max_blocks, page_shift, num_pages, num_rows, n_rows;
   int nh, nkv, window, split_size, max_splits, ring_slots, item_pages;
+  int chunk;                     // n > 0: the query (at position ctx_total - 1) sees only keys >= its position / n * n
+  const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
   float scale_log2;              // scale * log2(e)
   int* status;
   // Position encoding inside this kernel (`qkv` null: off; q then holds finished queries and the
@@ -110,9 +112,22 @@ struct ItemWalker {
   int tile, range, range_end, r;
 };
 
+// The first position the query at ctx_total - 1 sees: behind it lie a window, a chunk's start, or nothing.
+__device__ __forceinline__ int first_visible(int ctx_total, int window, int chunk) {
+  int lo = window > 0 ? max(0, ctx_total - window) : 0;
+  if (chunk > 0) lo = max(lo, (ctx_total - 1) / chunk * chunk);
+  return lo;
+}
+
+// exp2 of a head's sink relative to the maximum `mx` that a sum of exponentials is held against
+// (both in powers of two); 0 without sinks.
+__device__ __forceinline__ float sink_term(const float* sinks, int head, float mx) {
+  return sinks != nullptr ? exp2f(sinks[head] * 1.4426950408889634f - mx) : 0.0f;
+}
+
 // Positions [begin, end) of split `s` of a row; empty if begin >= end.
-__device__ __forceinline__ void split_range(int ctx_total, int window, int split_size, int s, int& begin, int& end) {
-  const int lo = window > 0 ? max(0, ctx_total - window) : 0;   // the query sits at ctx_total - 1
+__device__ __forceinline__ void split_range(int ctx_total, int window, int chunk, int split_size, int s, int& begin, int& end) {
+  const int lo = first_visible(ctx_total, window, chunk);
   begin = max(s * split_size, lo);
   end = min((s + 1) * split_size, ctx_total);
 }
@@ -141,11 +156,11 @@ __device__ __forceinline__ bool next_item(const DecodeArgs& a, const int* prefix
       it.row = a.rows[it.r];
       if (it.row < 0 || it.row >= a.num_rows) continue;            // reported when the kernel starts
       it.ctx_total = a.row_ctx[it.row] + 1;
-      split_range(it.ctx_total, a.window, a.split_size, split, it.begin, it.end);
+      split_range(it.ctx_total, a.window, a.chunk, a.split_size, split, it.begin, it.end);
       if (it.begin >= it.end) continue;
       it.first_tile = it.begin / DEC_TILE * DEC_TILE;
       it.n_tiles = (it.end - it.first_tile + DEC_TILE - 1) / DEC_TILE;
-      const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
+      const int lo = first_visible(it.ctx_total, a.window, a.chunk);
       const int first_split = lo / a.split_size, last_split = (it.ctx_total - 1) / a.split_size;
       it.n_parts = last_split - first_split + 1;
       it.merge_first = (it.r * a.nkv + it.kvh) * a.max_splits + first_split;
@@ -173,7 +188,7 @@ __device__ __forceinline__ bool next_item(const DecodeArgs& a, const int* prefix
     it.pair_start = prefix[w.r] + it.kvh * row_tiles;
     const int seg_end = min(w.range_end, static_cast<int>(it.pair_start) + row_tiles);
     it.ctx_total = a.row_ctx[it.row] + 1;
-    const int lo = a.window > 0 ? max(0, it.ctx_total - a.window) : 0;
+    const int lo = first_visible(it.ctx_total, a.window, a.chunk);
     const int first = lo / DEC_TILE + (w.tile - static_cast<int>(it.pair_start));   // the item's first tile of the row
     it.n_tiles = seg_end - w.tile;
     it.first_tile = first * DEC_TILE;
@@ -263,6 +278,8 @@ struct MergeJob {                        // what merge_many_parts needs of the l
   __nv_bfloat16* out;                    // the pair's first output element
   long long pair_start;
   int n_parts, merge_first, per_range, split_size, g;
+  const float* sinks;                    // null, or the launch's sinks
+  int head0;                             // the pair's first query head
   __device__ __forceinline__ int slot(int k) const {
     return split_size > 0 ? merge_first + k : balanced_slot(pair_start, merge_first + k, per_range);
   }
@@ -312,7 +329,7 @@ __device__ __noinline__ void merge_many_parts(const MergeJob job, float* merge_o
         ml_s[(k * g + h) * 2] = f;
       }
       lsum = warp_sum(lsum);
-      if (lane == 0) ml_s[it.n_parts * g * 2 + h] = lsum;
+      if (lane == 0) ml_s[it.n_parts * g * 2 + h] = lsum + sink_term(job.sinks, job.head0 + h, mx);
     }
     consumer_barrier();
     for (int v0 = 0; v0 < n_vec; v0 += per_group) {         // the same number of turns for every thread: barriers inside
@@ -423,7 +440,7 @@ paged_decode_kernel(const DecodeArgs a) {
       int tiles = 0;
       if (ok) {
         const int ctx_total = (row == r ? guess : a.row_ctx[row]) + 1;
-        const int lo = a.window > 0 ? max(0, ctx_total - a.window) : 0;
+        const int lo = first_visible(ctx_total, a.window, a.chunk);
         tiles = (ctx_total + DEC_TILE - 1) / DEC_TILE - lo / DEC_TILE;
       }
       prefix[r + 1] = tiles * a.nkv;
@@ -786,6 +803,7 @@ paged_decode_kernel(const DecodeArgs a) {
         l += merge_ml[(w * g + h) * 2 + 1] * f;
       }
       if (alone) {               // the only split of its row: this is the result
+        l += sink_term(a.sinks, it.kvh * g + h, mx);
         a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
       } else {
         const size_t slot = static_cast<size_t>(it.my_slot) * g + h;
@@ -820,6 +838,7 @@ paged_decode_kernel(const DecodeArgs a) {
       job.part_o = a.part_o; job.part_ml = a.part_ml; job.out = a.out + out_base;
       job.pair_start = it.pair_start;
       job.n_parts = it.n_parts; job.merge_first = it.merge_first; job.per_range = per_range; job.split_size = a.split_size; job.g = g;
+      job.sinks = a.sinks; job.head0 = it.kvh * g;
       merge_many_parts<HD>(job, merge_o);
     } else {
       for (int e = ctid; e < g * HD; e += DEC_CONSUMERS * 32) {
@@ -846,6 +865,7 @@ paged_decode_kernel(const DecodeArgs a) {
             acc += po[k] * f;
             l += pl[k] * f;
           }
+          l += sink_term(a.sinks, it.kvh * g + h, mx);
         } else {
           float mx = -INFINITY;
           for (int k = 0; k < it.n_parts; ++k)
@@ -856,6 +876,7 @@ paged_decode_kernel(const DecodeArgs a) {
             acc += __ldcg(&a.part_o[slot * HD + d]) * f;
             l += __ldcg(&a.part_ml[slot * 2 + 1]) * f;
           }
+          l += sink_term(a.sinks, it.kvh * g + h, mx);
         }
         a.out[out_base + e] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
       }
@@ -968,9 +989,9 @@ static int paged_decode_entry(void* out, const void* q, const void* kv_cache, co
                               int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
                               const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
                               float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
-                              const DecodeFusion* fusion, void* stream) {
+                              const DecodeFusion* fusion, void* stream, int chunk = 0, const float* sinks = nullptr) {
   if (n_rows < 0 || max_splits <= 0 || split_size < 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0 ||
-      counters == nullptr)
+      chunk < 0 || counters == nullptr)
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_decode_supported(nh, nkv, hd, DTYPE_BF16) || (page_size & (page_size - 1)) != 0) return ERR_UNSUPPORTED;
   if (n_rows == 0) return OK;
@@ -989,6 +1010,7 @@ static int paged_decode_entry(void* out, const void* q, const void* kv_cache, co
   a.max_blocks = max_blocks; a.page_shift = page_shift; a.num_pages = num_pages; a.num_rows = num_rows;
   a.n_rows = n_rows;
   a.nh = nh; a.nkv = nkv; a.window = window; a.split_size = split_size; a.max_splits = max_splits;
+  a.chunk = chunk; a.sinks = sinks;
   a.trace = decode_trace();
   a.qkv = nullptr;
   a.qkv_stride = 0;
@@ -1032,6 +1054,17 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
   return paged_decode_entry(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
                             row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, counters,
                             status, nullptr, stream);
+}
+
+// The same with a chunked mask and sinks, as in the general kernel (attention_simt.cu).
+ZB_API int zb_paged_decode_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                  int max_blocks, int page_size, int num_pages, int num_rows, const int* rows,
+                                  int n_rows, const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd,
+                                  int window, int chunk, float scale, const float* sinks, int split_size,
+                                  int max_splits, float* scratch, int* counters, int* status, void* stream) {
+  return paged_decode_entry(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
+                            row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, counters,
+                            status, nullptr, stream, chunk, sinks);
 }
 
 // The same with the new tokens' position encoding inside the kernel: `qkv` [T, qkv_stride] holds each

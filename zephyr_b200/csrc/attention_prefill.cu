@@ -32,6 +32,8 @@ struct PrefillArgs {
   const int* row_ctx;            // [R]
   int max_blocks, page_size, num_pages, num_rows;
   int nh, nkv, window;
+  int chunk;                     // n > 0: a query at position p sees only keys >= (p / n) * n
+  const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
   float scale_log2;
   int* status;
 };
@@ -66,7 +68,8 @@ paged_prefill_kernel(const PrefillArgs a) {
 
   // Keys any query of this tile may see: [lo, hi).
   const int hi = ctx + q0 + n_tok;
-  const int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
+  int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
+  if (a.chunk > 0) lo = max(lo, (ctx + q0) / a.chunk * a.chunk);
   const int first_tile = lo / PRE_BN * PRE_BN;
   const int n_tiles = (hi - first_tile + PRE_BN - 1) / PRE_BN;
 
@@ -108,7 +111,9 @@ paged_prefill_kernel(const PrefillArgs a) {
   const bool warp_active = warp_row0 < n_tok;
   const int qpos[2] = {ctx + q0 + warp_row0 + quad_row, ctx + q0 + warp_row0 + quad_row + 8};
   const int warp_last_pos = ctx + q0 + min(warp_row0 + 15, n_tok - 1);
-  const int warp_first_visible = a.window > 0 ? max(0, ctx + q0 + warp_row0 - a.window + 1) : 0;
+  int warp_first_visible = a.window > 0 ? max(0, ctx + q0 + warp_row0 - a.window + 1) : 0;
+  if (a.chunk > 0) warp_first_visible = max(warp_first_visible, (ctx + q0 + warp_row0) / a.chunk * a.chunk);
+  const int chunk_start[2] = {a.chunk > 0 ? qpos[0] / a.chunk * a.chunk : 0, a.chunk > 0 ? qpos[1] / a.chunk * a.chunk : 0};
 
   unsigned qa[HD / 16][4];
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
@@ -151,7 +156,7 @@ paged_prefill_kernel(const PrefillArgs a) {
       for (int c = 0; c < 4; ++c) {
         const int pos = k0 + nt * 8 + quad_col + (c & 1);
         const int qp = qpos[c >> 1];
-        const bool valid = pos <= qp && pos >= lo && (a.window == 0 || pos > qp - a.window);
+        const bool valid = pos <= qp && pos >= lo && (a.window == 0 || pos > qp - a.window) && pos >= chunk_start[c >> 1];
         s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
         tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
       }
@@ -208,7 +213,10 @@ paged_prefill_kernel(const PrefillArgs a) {
   for (int h = 0; h < 2; ++h) {
     const int r = warp_row0 + quad_row + 8 * h;
     if (r >= n_tok) continue;
-    const float inv = l_run[h] > 0.0f ? 1.0f / l_run[h] : 0.0f;
+    float denominator = l_run[h];
+    if (a.sinks != nullptr)      // one more exponential, relative to the running maximum (both in powers of two)
+      denominator += exp2f(a.sinks[head] * 1.4426950408889634f - m_run[h]);
+    const float inv = denominator > 0.0f ? 1.0f / denominator : 0.0f;
     __nv_bfloat16* dst = a.out + (static_cast<size_t>(tok0 + r) * a.nh + head) * HD + quad_col;
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n)
@@ -239,11 +247,13 @@ ZB_API int zb_paged_prefill_supported(int nh, int nkv, int hd, int dtype) {
 }
 
 // Attention of the tiles' tokens over their requests' pages; writes those tokens' rows of `out`.
-ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
-                            int page_size, int num_pages, int num_rows, const int* tile_row, const int* tile_q0,
-                            int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
-                            int nkv, int hd, int window, float scale, int* status, void* stream) {
-  if (n_tiles < 0 || page_size <= 0 || window < 0) return ERR_BAD_ARGUMENT;
+// `chunk` and `sinks` as in the general kernel (attention_simt.cu).
+ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                   int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
+                                   const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
+                                   const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
+                                   const float* sinks, int* status, void* stream) {
+  if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0) return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   if (n_tiles > 65535) return ERR_UNSUPPORTED;
@@ -254,7 +264,7 @@ ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, cons
   a.block_table = block_table; a.tile_row = tile_row; a.tile_q0 = tile_q0;
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
-  a.nh = nh; a.nkv = nkv; a.window = window;
+  a.nh = nh; a.nkv = nkv; a.window = window; a.chunk = chunk; a.sinks = sinks;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
@@ -264,4 +274,13 @@ ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, cons
     case 96: return prefill_launch<96>(a, n_tiles, s);
     default: return prefill_launch<128>(a, n_tiles, s);
   }
+}
+
+ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                            int page_size, int num_pages, int num_rows, const int* tile_row, const int* tile_q0,
+                            int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
+                            int nkv, int hd, int window, float scale, int* status, void* stream) {
+  return zb_paged_prefill_masked(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, tile_row,
+                                 tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, 0, scale,
+                                 nullptr, status, stream);
 }

@@ -87,6 +87,12 @@ _SIGNATURES = {
     "zb_paged_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p],
+    "zb_paged_decode_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p, c_void_p],
+    "zb_paged_prefill_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                c_void_p, c_void_p, c_void_p],
     "zb_paged_decode_fused": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
@@ -765,8 +771,10 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
                  row_q_start: torch.Tensor, row_ctx: torch.Tensor, max_context: int, nh: int, nkv: int, hd: int,
                  window: int, scale: float, status: torch.Tensor, out: torch.Tensor,
                  scratch: torch.Tensor | None = None, split_size: int | None = None,
-                 counters: torch.Tensor | None = None) -> torch.Tensor:
+                 counters: torch.Tensor | None = None, chunk: int = 0,
+                 sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Split-context attention for rows with one new token each; writes those tokens' rows of ``out``.
+    ``chunk`` and ``sinks`` as in ``paged_attention``.
 
     ``max_context`` is at least the longest context of the rows, the new token included.  ``scratch``
     (float32, any contents) and ``counters`` (int32, zero) come from a process-wide workspace unless
@@ -794,6 +802,16 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
              f"scratch must hold {need} floats")
     _require(counters.dtype == torch.int32 and counters.is_contiguous() and counters.numel() >= n_rows * nkv,
              f"counters must hold {n_rows * nkv} zeroed int32 values")
+    if chunk or sinks is not None:
+        _cuda(sinks)
+        _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
+                 "one float32 sink per query head")
+        _check(library().zb_paged_decode_masked(
+            _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+            block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
+            int(chunk), float(scale), _ptr(sinks), int(split_size), max_splits, _ptr(scratch), _ptr(counters),
+            _ptr(status), _stream()), "paged_decode")
+        return out
     _check(library().zb_paged_decode(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
@@ -886,14 +904,25 @@ def paged_prefill_supported(nh: int, nkv: int, hd: int, dtype: torch.dtype) -> b
 def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
                   tile_q0: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx: torch.Tensor,
                   nh: int, nkv: int, hd: int, window: int, scale: float, status: torch.Tensor,
-                  out: torch.Tensor) -> torch.Tensor:
+                  out: torch.Tensor, chunk: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
     """Tensor-core attention for rows with several new tokens, cut into tiles of
-    ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``."""
+    ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk`` and ``sinks`` as in
+    ``paged_attention``; with either the mma.sync kernel runs, at every head size."""
     _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out)
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    if chunk or sinks is not None:
+        _cuda(sinks)
+        _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
+                 "one float32 sink per query head")
+        _check(library().zb_paged_prefill_masked(
+            _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+            block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
+            _ptr(row_ctx), nh, nkv, hd, int(window), int(chunk), float(scale), _ptr(sinks), _ptr(status), _stream()),
+            "paged_prefill")
+        return out
     # Head size 128 runs on tcgen05 with the accumulators in tensor memory; other sizes on mma.sync.
     tensor_memory = USE_TCGEN05_PREFILL and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype],
                                                                                      page_size))

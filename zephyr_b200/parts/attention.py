@@ -116,7 +116,13 @@ class Attention(Mixer):
         self.score_slopes = None
         self.group = self.nh // self.nkv
         self.tile_tokens = ops.attention_tile_tokens(self.group)
-        self.fast_decode = self.fast_prefill = self.fused_position = False
+        self.fused_position = False
+        # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask and sinks
+        # too, for keys and values of one width in bfloat16; everything else stays with the general kernel.
+        equal = self.vd == self.hd
+        self.fast_decode = equal and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
+        self.fast_prefill = equal and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, self.dtype)
+        self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     def score_slopes_wanted(self) -> bool:
         return self.position is not None and self.position.as_score_slopes() is not None
@@ -201,26 +207,27 @@ class Attention(Mixer):
         goes to the general kernel."""
         cache = ctx.caches[call.cache]
         table = ctx.block_table(call.cache)
-        out = torch.empty_like(q)
+        out = torch.empty((q.shape[0], self.nh * self.vd), dtype=q.dtype, device=q.device)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
+        masks = {"chunk": self.chunk, "sinks": self.sinks} if (self.chunk or self.sinks is not None) else {}
         decode_done = self.fast_decode and ctx.num_decode_rows > 0
         if decode_done:
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
-                             *common, out=out)
+                             *common, out=out, **masks)
         prefill_done = False
         if self.fast_prefill:
             tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "multi")]
             prefill_done = True
             if tile_row.numel() > 0:
                 ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,
-                                  *common, out=out)
+                                  *common, out=out, **masks)
         if decode_done and prefill_done:
             return out
         which = "multi" if decode_done else ("single" if prefill_done else "all")
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
-                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes)
+                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks)
         return out
 
     takes_out_dtype = True
@@ -239,11 +246,7 @@ class Attention(Mixer):
         q = ops.qkv_pairs(projected, self.nh, self.nkv, self.hd, self.vd, bias, self.q_norm, self.k_norm, self.eps,
                           self.pair_freqs, self.pair_dims, ctx.positions, ctx.token_row, cache, table, ctx.status,
                           self.dtype)
-        tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
-        attended = ops.paged_attention(q, ctx.caches[call.cache], table, tile_row, tile_q0, self.tile_tokens,
-                                       ctx.row_q_start, ctx.row_q_len, ctx.row_ctx, self.nh, self.nkv, self.hd,
-                                       self.window, self.scale, ctx.status, value_dim=self.vd, chunk=self.chunk,
-                                       sinks=self.sinks)
+        attended = self.attend(q, ctx, call)
         return ops.linear(attended, self.w_o, out_dtype=out_dtype, bias=self.o_bias)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
