@@ -359,7 +359,10 @@ def test_chunked_sink_attention_at_its_edges(cuda_device, dtype, kd, vd, heads, 
         if target < 0:
             continue
         targets[p] = target
-        q[p, 0] = k[target, 0] * 8.0           # a match: a score of 8 kd against about 8 sqrt(kd) for the rest
+    for target in set(targets.values()):
+        k[target, 0] *= 4.0                        # a long key, so that the match below beats every chance alignment
+    for p, target in targets.items():
+        q[p, 0] = k[target, 0] * 2.0               # a score of 32 |k|^2 against about 8 |k| |k'| cos for the rest
     sinks = torch.randn(heads, generator=g)
     sinks[-1] = 80.0                            # the last head gives nearly everything to its sink
     freqs = plain_rotary_frequencies({"base": 100.0, "dims": rot_dims}) if rot_dims else None
