@@ -37,6 +37,16 @@ SHAPES = {      # the layer sizes of the Qwen3 family members the benchmark name
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
+# ``--arch legelix``: layer sizes of the kind a model of a few billion parameters has, for the design whose
+# layers alternate gated linear attention with attention and Mamba-2 side by side, each beside the Qwen3
+# decoder of the same width, feed-forward, head counts and number of layers.
+LEGELIX_SIZES = {
+    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, kv_heads=8, head_dim=128, chunk=1024,
+                  gla=dict(heads=8, dim=128, vdim=256), ssm=dict(heads=32, vdim=64, state=128, groups=2)),
+    "w4096": dict(width=4096, ff=12288, layers=8, heads=32, kv_heads=8, head_dim=128, chunk=2048,
+                  gla=dict(heads=16, dim=128, vdim=256), ssm=dict(heads=64, vdim=64, state=128, groups=4)),
+}
+
 
 def metric_name(args) -> str:
     """One string for both arms: the driver divides their values only if the strings are equal."""
@@ -160,6 +170,66 @@ def build_engine(shape: str, layers: int | None, batch: int, context: int, dtype
         raise SystemExit(f"bench.py: the cache pool got {engine.runner.manager.groups[0].pool.num_usable} pages, "
                          f"{needed} are needed for batch {batch} at context {context}")
     return engine, config, full_layers
+
+
+def build_pair(size: str, batch: int, context: int):
+    """(Legelix engine, Qwen3 engine builder) of one entry of ``LEGELIX_SIZES``; random weights, bfloat16."""
+    import torch
+
+    from zephyr_b200 import Engine
+    from zephyr_b200.config import LegelixConfig, Qwen3Config
+    from zephyr_b200.engine import KvCacheOptions, PagedSchedulerConfig
+    from zephyr_b200.parts import expected_weights
+    from zephyr_b200.weights import RandomWeights
+
+    z = LEGELIX_SIZES[size]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    gla = {"type": "gla", "mixer": dict(tau=16.0, **z["gla"]), "mlp": mlp}
+    left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head_dim"], vdim=z["head_dim"], scale=z["head_dim"] ** -0.5,
+                mask={"size": z["chunk"]}, rot={"base": 500000.0, "dims": z["head_dim"],
+                                                "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    both = {"type": "parallel", "mlp": mlp, "mixer": {"left": left, "right": dict(conv=4, norm_groups=2, **z["ssm"]),
+                                                      "left_scale": 1.0, "right_scale": 1.0}}
+    legelix = LegelixConfig(vocab=32768, width=z["width"], layers=tuple([gla, both] * (z["layers"] // 2)), norm_eps=1e-6,
+                            residual_mult=0.5, decay_rank=16)
+    qwen = Qwen3Config(max_position_embeddings=max(context, 4096), rms_norm_eps=1e-6, rope_theta=1000000.0,
+                       num_hidden_layers=z["layers"], hidden_size=z["width"], num_attention_heads=z["heads"],
+                       num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"], intermediate_size=z["ff"],
+                       vocab_size=32768, tie_word_embeddings=False)
+
+    def make(config):
+        store = RandomWeights(expected_weights(config.to_model_spec()), seed=0, dtype=torch.bfloat16, device="cuda")
+        return Engine(None, dtype="bfloat16", model_config=config, weights=store, max_seq_len=context,
+                      kv_cache=KvCacheOptions(block_size=PAGE_SIZE, num_blocks=(batch + 1) * -(-context // PAGE_SIZE) + 1),
+                      scheduler=PagedSchedulerConfig(max_num_seqs=batch + 1, max_num_batched_tokens=max(PREFILL_TOKENS, batch),
+                                                     max_prefill_chunk_tokens=PREFILL_TOKENS))
+    return legelix, qwen, make
+
+
+def run_legelix(args) -> dict:
+    """Prefill of 2048 tokens and a decode step of ``--batch`` requests at ``--context``, device-timed, for
+    every entry of ``LEGELIX_SIZES`` and for the Qwen3 decoder of equal size beside it."""
+    import gc
+
+    import torch
+
+    out = {"arch": "legelix", "batch": args.batch, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
+           "data": "synthetic: seeded random weights and token ids", "sizes": {}}
+    for size in (args.sizes.split(",") if args.sizes else LEGELIX_SIZES):
+        legelix, qwen, make = build_pair(size, args.batch, args.context)
+        row = {}
+        for name, config in (("legelix", legelix), ("qwen3", qwen)):
+            engine = make(config)
+            prefill_ms = device_prefill(engine, PREFILL_TOKENS, 3, 5)
+            decode_ms, launches, _ = device_decode(engine, args.batch, args.context, args.warmup, args.steps, None)
+            row[name] = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1e3),
+                         "decode_ms_per_step": round(decode_ms, 4), "decode_tok_s": round(args.batch / decode_ms * 1e3),
+                         "gpu_launches": launches, "weights_gb": round(engine.model.weight_bytes_read_per_step() / 1e9, 3)}
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    return out
 
 
 def model_flops_per_token(config) -> float:
@@ -446,6 +516,9 @@ def main() -> int:
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
     parser.add_argument("--own-products", action="store_true",
                         help="with --only: no product on the vendor library (all on this package's tcgen05 kernel)")
+    parser.add_argument("--arch", choices=("qwen3", "legelix"), default="qwen3",
+                        help="legelix: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal size")
+    parser.add_argument("--sizes", default="", help="--arch legelix: entries of LEGELIX_SIZES, with commas (default: all)")
     parser.add_argument("--only", choices=("prefill", "decode"), default=None,
                         help="time only the 2048-token prefill, or only the decode step, and print a short line "
                              "(the program a profiler is pointed at)")
@@ -455,6 +528,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.arch == "legelix":
+        print(json.dumps(run_legelix(args)))
+        return 0
     if args.only is not None and args.impl == "ours":
         if args.own_products:
             from zephyr_b200.kernels import ops

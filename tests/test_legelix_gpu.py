@@ -311,7 +311,7 @@ def test_state_space_recurrence_convolution_and_gated_norm(cuda_device):
             starts, lens = _rows([n], cuda_device)
             slots = torch.tensor([slot], dtype=torch.int32, device=cuda_device)
             m = ops.causal_conv_silu(part[:, inner:], channels, dev(conv_w), dev(conv_b), store[:, scan:], slots, starts,
-                                     lens, status)
+                                     lens, torch.zeros(n, dtype=torch.int32, device=cuda_device), status)
             assert (m.cpu().double() - mixed[at:at + n]).abs().max() < 1e-5
             o = ops.decayed_state_scan("state_space", m[:, inner + gn:], m[:, inner:inner + gn], m[:, :inner], heads, N,
                                        vdim, store[:, :scan], slots, starts, lens, status, dt=part[:, inner + channels:],

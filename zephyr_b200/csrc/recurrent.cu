@@ -14,6 +14,8 @@
 // Everything that enters the recurrence is float32: decays, their logarithms, softplus, step sizes,
 // the state, the sums.  A row's tokens are run in their order, so a result does not depend on how a
 // prompt was cut into steps or on what else a step carries.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace zb {
@@ -89,9 +91,9 @@ __global__ void embedding_f32_kernel(float* out, const T* table, const int* ids,
 }
 
 // ------------------------------------------------------------------------------------------------
-// Causal convolution per channel with SiLU.  A thread owns a channel of one request and walks that
-// request's new tokens in order with the last `taps` inputs in registers; the window starts from the
-// request's state (zeros for a new request) and its last taps - 1 inputs go back there.
+// Causal convolution per channel with SiLU, over all new tokens of the step at once; the inputs before
+// a request's first new token come from its state (zeros for a new request), and a second small
+// kernel then puts the request's last taps - 1 inputs there.
 constexpr int CONV_MAX_TAPS = 8;
 
 struct ConvArgs {
@@ -109,63 +111,91 @@ struct ConvArgs {
   int* status;
 };
 
+// The convolution proper: a thread owns a channel of one token (CONV_TOKENS consecutive ones) of the
+// step's stream.  Input i of a request's new tokens is row t0 + i of x for i >= 0 and entry taps - 1 + i of
+// the request's state for i < 0; nothing is written to the state here.
+constexpr int CONV_TOKENS = 1;
+
 template <typename T>
-__global__ void causal_conv_silu_kernel(const ConvArgs a) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+__global__ void causal_conv_silu_kernel(const ConvArgs a, const int* token_row, int tokens) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= a.C) return;
-  const int slot = a.slots[row];
-  if (slot < 0 || slot >= a.num_slots) {
-    report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
-    return;
-  }
-  const int first = CONV_MAX_TAPS - a.taps;          // window entries before `first` stay zero
-  float win[CONV_MAX_TAPS], w[CONV_MAX_TAPS];
-  float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
+  float w[CONV_MAX_TAPS];
 #pragma unroll
-  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-    w[j] = j >= first ? load_scale(a.w, a.w_dtype, c * a.taps + (j - first)) : 0.0f;
-    // win[j + 1] is what win[j] will be after the first shift
-    win[j] = (j > first) ? state[static_cast<long long>(j - first - 1) * a.C + c] : 0.0f;
-  }
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j < a.taps ? load_scale(a.w, a.w_dtype, c * a.taps + j) : 0.0f;
   const float bias = load_scale(a.bias, a.w_dtype, c);
   const T* x = static_cast<const T*>(a.x);
   T* out = static_cast<T*>(a.out);
-  const int t0 = a.row_q_start[row], n = a.row_q_len[row];
-  for (int i = 0; i < n; ++i) {
-#pragma unroll
-    for (int j = 0; j + 1 < CONV_MAX_TAPS; ++j) win[j] = win[j + 1];
-    win[CONV_MAX_TAPS - 1] = to_float(x[static_cast<long long>(t0 + i) * a.x_stride + c]);
+  const int first = blockIdx.y * CONV_TOKENS;
+  for (int t = first; t < min(first + CONV_TOKENS, tokens); ++t) {
+    const int row = token_row[t];
+    const int slot = a.slots[row];
+    if (slot < 0 || slot >= a.num_slots) {
+      report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+      continue;
+    }
+    const int i = t - a.row_q_start[row];
+    const float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
     float acc = 0.0f;
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) acc = fmaf(w[j], win[j], acc);
-    out[static_cast<long long>(t0 + i) * a.C + c] = from_float<T>(silu_f(acc + bias));
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {          // oldest input first, as the weights lie
+      if (j < a.taps) {
+        const int back = a.taps - 1 - j;
+        const float in = i - back >= 0 ? to_float(x[static_cast<long long>(t - back) * a.x_stride + c])
+                                       : state[static_cast<long long>(a.taps - 1 + i - back) * a.C + c];
+        acc = fmaf(w[j], in, acc);
+      }
+    }
+    out[static_cast<long long>(t) * a.C + c] = from_float<T>(silu_f(acc + bias));
   }
-  if (a.write_state) {
+}
+
+// After it: every request's last taps - 1 inputs go to its state.  A thread owns a channel of one request.
+template <typename T>
+__global__ void conv_state_update_kernel(const ConvArgs a) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, row = blockIdx.y;
+  if (c >= a.C) return;
+  const int slot = a.slots[row];
+  if (slot < 0 || slot >= a.num_slots) return;       // reported by the convolution
+  float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
+  const T* x = static_cast<const T*>(a.x);
+  const int t0 = a.row_q_start[row], n = a.row_q_len[row], keep = a.taps - 1;
+  float last[CONV_MAX_TAPS];
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j)
-      if (j > first) state[static_cast<long long>(j - first - 1) * a.C + c] = win[j];
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+    if (j < keep) {
+      const int i = n - keep + j;                     // the input that becomes entry j
+      last[j] = i >= 0 ? to_float(x[static_cast<long long>(t0 + i) * a.x_stride + c])
+                       : state[static_cast<long long>(keep + i) * a.C + c];
+    }
   }
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j)
+    if (j < keep) state[static_cast<long long>(j) * a.C + c] = last[j];
 }
 
 // ------------------------------------------------------------------------------------------------
 // The recurrence.  A CTA owns one request, one head and 32 value columns; warp w owns the key
-// channels 32 w .. 32 w + 31 of those columns, each lane one column with its 32 state values in
-// registers.  The tokens of the request are taken SCAN_CHUNK at a time: decays, keys, queries and
-// values of the chunk are formed in shared memory (all float32), every warp runs the chunk's tokens
-// in order, and the warps' partial outputs are added in warp order.
-constexpr int SCAN_CHUNK = 8;
-constexpr int SCAN_ROWS = 32;        // key channels per warp
+// channels 16 w .. 16 w + 15 of those columns, each lane one column with its 16 state values in
+// registers (two warps per scheduler and more: one warp's shared-memory loads hide behind another's
+// multiply-adds).  The tokens of the request are taken SCAN_CHUNK at a time: decays, keys, queries and
+// values of the chunk lie in shared memory (all float32), every warp runs the chunk's tokens in
+// order, and the warps' partial outputs are added in warp order.  While a chunk runs, the next one's
+// inputs are already on their way into registers.  The gated form's decays are made beforehand, in
+// place of their logits, by a kernel of their own (every CTA of a head would otherwise repeat them).
+constexpr int SCAN_CHUNK = 16;
+constexpr int SCAN_ROWS = 16;        // key channels per warp
 constexpr int SCAN_COLS = 32;        // value columns per CTA
+constexpr int SCAN_V_REGS = SCAN_CHUNK * SCAN_COLS / 64;   // values a thread fetches ahead, at most (a CTA has two warps or more)
 
-constexpr int SCAN_GATED = 0;        // a[d] = sigmoid(z[d] + bias[d])^(1/tau), q scaled
+constexpr int SCAN_GATED = 0;        // a[d] given per key channel (made from the logits by gated_decay_kernel), q scaled
 constexpr int SCAN_STATE_SPACE = 1;  // a = exp(-exp(A_log[h]) dt), k = dt B, q = C, o += skip[h] v, dt = softplus(. + dt_bias[h])
 
 struct ScanArgs {
   const void* q; long long q_stride;   // [tokens, .]: head h (or its group) at column h * D
   const void* k; long long k_stride;
   const void* v; long long v_stride;   // [tokens, .]: head h at column h * V
-  const float* z; long long z_stride;  // gated: decay logits [tokens, H * D], float32
-  const void* z_bias;                  // gated: [H * D]
+  const float* z; long long z_stride;  // gated: decays [tokens, H * D], float32
   const void* dt; long long dt_stride; // state space: [tokens, H]
   const void* dt_bias; const void* a_log; const void* skip;   // state space: [H] each
   int w_dtype;
@@ -173,24 +203,36 @@ struct ScanArgs {
   float* out;                          // [tokens, H * V] float32
   const int* slots; const int* row_q_start; const int* row_q_len;
   int H, D, V, heads_per_group, num_slots, write_state;
-  float q_scale, inv_tau;
+  float q_scale;
   int* status;
 };
 
+// z <- sigmoid(z + bias)^(1/tau), through the logarithm: exp(log_sigmoid(z + bias) / tau).
+__global__ void gated_decay_kernel(float* z, long long z_stride, const void* bias, int w_dtype, int width, float inv_tau,
+                                   long long count) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const long long t = i / width;
+  const int c = static_cast<int>(i - t * width);
+  float* at = z + t * z_stride + c;
+  *at = expf(log_sigmoid_f(*at + load_scale(bias, w_dtype, c)) * inv_tau);
+}
+
 template <typename T, int MODE>
-__global__ void __launch_bounds__(256) decayed_state_scan_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs a) {
   extern __shared__ __align__(16) float scan_smem[];
-  const int D = a.D, V = a.V, nwarps = blockDim.x >> 5, Dp = nwarps * SCAN_ROWS;
-  float* a_s = scan_smem;                                   // [SCAN_CHUNK][Dp] (state space: one value per token)
+  const int D = a.D, V = a.V, nwarps = blockDim.x >> 5, Dp = nwarps * SCAN_ROWS;     // blockDim.x == 2 Dp
+  float* a_s = scan_smem;                                   // [SCAN_CHUNK][Dp]
   float* k_s = a_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][Dp]
   float* q_s = k_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][Dp]
   float* v_s = q_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][SCAN_COLS]
   float* o_s = v_s + SCAN_CHUNK * SCAN_COLS;                // [SCAN_CHUNK][nwarps][SCAN_COLS]
+  float* step_s = o_s + SCAN_CHUNK * nwarps * SCAN_COLS;    // [2][SCAN_CHUNK]: state space: step sizes, decays
   const int v0 = blockIdx.x * SCAN_COLS, h = blockIdx.y, row = blockIdx.z;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slot = a.slots[row];
   if (slot < 0 || slot >= a.num_slots) {
-    if (threadIdx.x == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+    if (tid == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
     return;
   }
   const int t0 = a.row_q_start[row], n = a.row_q_len[row];
@@ -212,56 +254,97 @@ __global__ void __launch_bounds__(256) decayed_state_scan_kernel(const ScanArgs 
     head_skip = load_scale(a.skip, a.w_dtype, h);
   }
 
+  // What this thread fetches ahead: one key channel of every second token of the chunk (the threads'
+  // two halves take the even and the odd tokens), a share of the values, and (state space, the first
+  // SCAN_CHUNK threads) a token's raw step size.
+  constexpr int PER = SCAN_CHUNK / 2;
+  const int my_d = tid < Dp ? tid : tid - Dp, my_t = tid < Dp ? 0 : 1;
+  // Keys, queries, values and step sizes stay in their own type until they are stored to shared memory:
+  // a conversion at the load would make the thread wait for the load there and then.
+  float pa[PER];
+  T pk[PER], pq[PER], pv[SCAN_V_REGS], pdt = from_float<T>(0.0f);
+  auto fetch = [&](int c0) {
+    const int nc = min(SCAN_CHUNK, n - c0);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int t = 2 * j + my_t;
+      pa[j] = 0.0f;
+      pk[j] = pq[j] = from_float<T>(0.0f);
+      if (t < nc && my_d < D) {
+        const long long tok = t0 + c0 + t;
+        pk[j] = kp[tok * a.k_stride + qk_col + my_d];
+        pq[j] = qp[tok * a.q_stride + qk_col + my_d];
+        if (MODE == SCAN_GATED) pa[j] = a.z[tok * a.z_stride + h * D + my_d];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SCAN_V_REGS; ++j) {
+      const int e = tid + j * static_cast<int>(blockDim.x);
+      pv[j] = from_float<T>(0.0f);
+      if (e < SCAN_CHUNK * SCAN_COLS) {
+        const int t = e / SCAN_COLS, c = v0 + (e - t * SCAN_COLS);
+        if (t < nc && c < V) pv[j] = vp[static_cast<long long>(t0 + c0 + t) * a.v_stride + h * V + c];
+      }
+    }
+    if (MODE == SCAN_STATE_SPACE && tid < nc)
+      pdt = static_cast<const T*>(a.dt)[static_cast<long long>(t0 + c0 + tid) * a.dt_stride + h];
+  };
+
+  if (n > 0) fetch(0);
   for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
     const int nc = min(SCAN_CHUNK, n - c0);
     __syncthreads();                      // the chunk before is no longer read
-    for (int e = threadIdx.x; e < SCAN_CHUNK * Dp; e += blockDim.x) {
-      const int t = e / Dp, d = e - t * Dp;
-      float av = 0.0f, kv = 0.0f, qv = 0.0f;
-      if (t < nc && d < D) {
-        const long long tok = t0 + c0 + t;
-        kv = to_float(kp[tok * a.k_stride + qk_col + d]);
-        qv = to_float(qp[tok * a.q_stride + qk_col + d]);
-        if (MODE == SCAN_GATED) {
-          const float z = a.z[tok * a.z_stride + h * D + d] + load_scale(a.z_bias, a.w_dtype, h * D + d);
-          av = expf(log_sigmoid_f(z) * a.inv_tau);
-          qv *= a.q_scale;
-        } else {
-          const float dt = softplus_f(to_float(static_cast<const T*>(a.dt)[tok * a.dt_stride + h]) + head_dt_bias);
-          av = expf(head_decay * dt);
-          kv *= dt;
-        }
+    if (MODE == SCAN_STATE_SPACE) {
+      if (tid < nc) {
+        const float dt = softplus_f(to_float(pdt) + head_dt_bias);
+        step_s[tid] = dt;
+        step_s[SCAN_CHUNK + tid] = expf(head_decay * dt);
       }
-      a_s[e] = av;
-      k_s[e] = kv;
-      q_s[e] = qv;
+      __syncthreads();
     }
-    for (int e = threadIdx.x; e < SCAN_CHUNK * SCAN_COLS; e += blockDim.x) {
-      const int t = e / SCAN_COLS, c = v0 + (e - t * SCAN_COLS);
-      v_s[e] = (t < nc && c < V) ? to_float(vp[static_cast<long long>(t0 + c0 + t) * a.v_stride + h * V + c]) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int t = 2 * j + my_t, e = t * Dp + my_d;
+      if (MODE == SCAN_GATED) {
+        a_s[e] = pa[j];
+        k_s[e] = to_float(pk[j]);
+        q_s[e] = to_float(pq[j]) * a.q_scale;
+      } else {
+        a_s[e] = t < nc ? step_s[SCAN_CHUNK + t] : 0.0f;
+        k_s[e] = t < nc ? to_float(pk[j]) * step_s[t] : 0.0f;
+        q_s[e] = to_float(pq[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < SCAN_V_REGS; ++j) {
+      const int e = tid + j * static_cast<int>(blockDim.x);
+      if (e < SCAN_CHUNK * SCAN_COLS) v_s[e] = to_float(pv[j]);
     }
     __syncthreads();
+    if (c0 + SCAN_CHUNK < n) fetch(c0 + SCAN_CHUNK);      // lands while this chunk runs
     for (int t = 0; t < nc; ++t) {
       const float vt = v_s[t * SCAN_COLS + lane];
-      const float* at = a_s + t * Dp + d0;
-      const float* kt = k_s + t * Dp + d0;
-      const float* qt = q_s + t * Dp + d0;
+      const float4* at = reinterpret_cast<const float4*>(a_s + t * Dp + d0);
+      const float4* kt = reinterpret_cast<const float4*>(k_s + t * Dp + d0);
+      const float4* qt = reinterpret_cast<const float4*>(q_s + t * Dp + d0);
       float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
 #pragma unroll
-      for (int d = 0; d < SCAN_ROWS; d += 4) {
-        S[d] = fmaf(at[d], S[d], kt[d] * vt);
-        o0 = fmaf(S[d], qt[d], o0);
-        S[d + 1] = fmaf(at[d + 1], S[d + 1], kt[d + 1] * vt);
-        o1 = fmaf(S[d + 1], qt[d + 1], o1);
-        S[d + 2] = fmaf(at[d + 2], S[d + 2], kt[d + 2] * vt);
-        o2 = fmaf(S[d + 2], qt[d + 2], o2);
-        S[d + 3] = fmaf(at[d + 3], S[d + 3], kt[d + 3] * vt);
-        o3 = fmaf(S[d + 3], qt[d + 3], o3);
+      for (int d4 = 0; d4 < SCAN_ROWS / 4; ++d4) {
+        const float4 av = at[d4], kv = kt[d4], qv = qt[d4];
+        const int d = 4 * d4;
+        S[d] = fmaf(av.x, S[d], kv.x * vt);
+        o0 = fmaf(S[d], qv.x, o0);
+        S[d + 1] = fmaf(av.y, S[d + 1], kv.y * vt);
+        o1 = fmaf(S[d + 1], qv.y, o1);
+        S[d + 2] = fmaf(av.z, S[d + 2], kv.z * vt);
+        o2 = fmaf(S[d + 2], qv.z, o2);
+        S[d + 3] = fmaf(av.w, S[d + 3], kv.w * vt);
+        o3 = fmaf(S[d + 3], qv.w, o3);
       }
       o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < nc * SCAN_COLS; e += blockDim.x) {
+    for (int e = tid; e < nc * SCAN_COLS; e += blockDim.x) {
       const int t = e / SCAN_COLS, l = e - t * SCAN_COLS, c = v0 + l;
       if (c >= V) continue;
       float o = 0.0f;
@@ -388,7 +471,8 @@ ZB_API int zb_embedding_f32(float* out, const void* table, const int* ids, int t
 }
 
 ZB_API int zb_causal_conv_silu(void* out, const void* x, long long x_stride, float* state, long long slot_stride,
-                               const int* slots, const int* row_q_start, const int* row_q_len, int rows, const void* w,
+                               const int* slots, const int* row_q_start, const int* row_q_len, const int* token_row,
+                               int tokens, int rows, const void* w,
                                const void* bias, int w_dtype, int C, int taps, int num_slots, int write_state, int dtype,
                                int* status, void* stream) {
   if (rows < 0 || C <= 0 || taps <= 0) return ERR_BAD_ARGUMENT;
@@ -399,43 +483,60 @@ ZB_API int zb_causal_conv_silu(void* out, const void* x, long long x_stride, flo
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.w = w; a.bias = bias; a.w_dtype = w_dtype; a.C = C;
   a.taps = taps; a.num_slots = num_slots; a.write_state = write_state; a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
-  const dim3 grid((C + 127) / 128, rows);
-  if (dtype == DTYPE_F32) causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>(a);
-  else causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a);
+  if (tokens <= 0) return OK;
+  const dim3 grid((C + 127) / 128, (tokens + CONV_TOKENS - 1) / CONV_TOKENS), per_row((C + 127) / 128, rows);
+  if (dtype == DTYPE_F32) {
+    causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>(a, token_row, tokens);
+    if (write_state && taps > 1) conv_state_update_kernel<float><<<per_row, 128, 0, s>>>(a);
+  } else {
+    causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a, token_row, tokens);
+    if (write_state && taps > 1) conv_state_update_kernel<__nv_bfloat16><<<per_row, 128, 0, s>>>(a);
+  }
   return launch_result();
 }
 
 // The most key channels a head of the recurrence may have.
-ZB_API int zb_state_scan_max_channels() { return 8 * SCAN_ROWS; }
+ZB_API int zb_state_scan_max_channels() { return 16 * SCAN_ROWS; }
 
+// `z` (gated mode): decay logits [tokens, H * D] float32, overwritten with the decays.
 ZB_API int zb_decayed_state_scan(float* out, const void* q, long long q_stride, const void* k, long long k_stride,
-                                 const void* v, long long v_stride, const float* z, long long z_stride,
+                                 const void* v, long long v_stride, float* z, long long z_stride,
                                  const void* z_bias, const void* dt, long long dt_stride, const void* dt_bias,
                                  const void* a_log, const void* skip, int w_dtype, float* state, long long slot_stride,
-                                 const int* slots, const int* row_q_start, const int* row_q_len, int rows, int H, int D,
-                                 int V, int heads_per_group, int num_slots, int write_state, float q_scale,
-                                 float inv_tau, int mode, int dtype, int* status, void* stream) {
-  if (rows < 0 || H <= 0 || D <= 0 || V <= 0 || heads_per_group <= 0) return ERR_BAD_ARGUMENT;
-  if (D > 8 * SCAN_ROWS) return ERR_UNSUPPORTED;
+                                 const int* slots, const int* row_q_start, const int* row_q_len, int rows, int tokens,
+                                 int H, int D, int V, int heads_per_group, int num_slots, int write_state,
+                                 float q_scale, float inv_tau, int mode, int dtype, int* status, void* stream) {
+  if (rows < 0 || tokens < 0 || H <= 0 || D <= 0 || V <= 0 || heads_per_group <= 0) return ERR_BAD_ARGUMENT;
+  if (D > 16 * SCAN_ROWS) return ERR_UNSUPPORTED;
   if (mode != SCAN_GATED && mode != SCAN_STATE_SPACE) return ERR_BAD_ARGUMENT;
-  if (rows == 0) return OK;
+  if (rows == 0 || tokens == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (mode == SCAN_GATED) {
+    const long long count = static_cast<long long>(tokens) * H * D;
+    gated_decay_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, s>>>(z, z_stride, z_bias, w_dtype, H * D,
+                                                                                inv_tau, count);
+  }
   ScanArgs a;
   a.q = q; a.q_stride = q_stride; a.k = k; a.k_stride = k_stride; a.v = v; a.v_stride = v_stride;
-  a.z = z; a.z_stride = z_stride; a.z_bias = z_bias; a.dt = dt; a.dt_stride = dt_stride; a.dt_bias = dt_bias;
+  a.z = z; a.z_stride = z_stride; a.dt = dt; a.dt_stride = dt_stride; a.dt_bias = dt_bias;
   a.a_log = a_log; a.skip = skip; a.w_dtype = w_dtype; a.state = state; a.slot_stride = slot_stride; a.out = out;
   a.slots = slots; a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.H = H; a.D = D; a.V = V;
   a.heads_per_group = heads_per_group; a.num_slots = num_slots; a.write_state = write_state; a.q_scale = q_scale;
-  a.inv_tau = inv_tau; a.status = status;
-  const int warps = (D + SCAN_ROWS - 1) / SCAN_ROWS;
+  a.status = status;
+  const int warps = std::max(2, (D + SCAN_ROWS - 1) / SCAN_ROWS);
   const size_t smem = sizeof(float) * (3 * SCAN_CHUNK * warps * SCAN_ROWS + SCAN_CHUNK * SCAN_COLS +
-                                       SCAN_CHUNK * warps * SCAN_COLS);
+                                       SCAN_CHUNK * warps * SCAN_COLS + 2 * SCAN_CHUNK);
   const dim3 grid((V + SCAN_COLS - 1) / SCAN_COLS, H, rows);
-  auto s = static_cast<cudaStream_t>(stream);
-#define ZB_SCAN(T, MODE) decayed_state_scan_kernel<T, MODE><<<grid, warps * 32, smem, s>>>(a)
+#define ZB_SCAN(T, MODE)                                              \
+  {                                                                   \
+    auto kernel = decayed_state_scan_kernel<T, MODE>;                 \
+    if (int rc = allow_shared(kernel, smem)) return rc;               \
+    kernel<<<grid, warps * 32, smem, s>>>(a);                         \
+  }
   if (dtype == DTYPE_F32) {
-    if (mode == SCAN_GATED) ZB_SCAN(float, SCAN_GATED); else ZB_SCAN(float, SCAN_STATE_SPACE);
+    if (mode == SCAN_GATED) ZB_SCAN(float, SCAN_GATED) else ZB_SCAN(float, SCAN_STATE_SPACE)
   } else {
-    if (mode == SCAN_GATED) ZB_SCAN(__nv_bfloat16, SCAN_GATED); else ZB_SCAN(__nv_bfloat16, SCAN_STATE_SPACE);
+    if (mode == SCAN_GATED) ZB_SCAN(__nv_bfloat16, SCAN_GATED) else ZB_SCAN(__nv_bfloat16, SCAN_STATE_SPACE)
   }
 #undef ZB_SCAN
   return launch_result();

@@ -73,12 +73,13 @@ _SIGNATURES = {
     "zb_residual_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
                                c_float, c_float, c_int, c_int, c_int, c_void_p],
     "zb_embedding_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
-    "zb_causal_conv_silu": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
-                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_causal_conv_silu": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                            c_void_p],
     "zb_state_scan_max_channels": [],
     "zb_decayed_state_scan": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                              c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_float, c_float, c_int, c_int, c_void_p, c_void_p],
     "zb_gated_group_rms_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_float, c_int, c_int, c_void_p],
@@ -410,15 +411,16 @@ CONV_MAX_TAPS = 8
 
 
 def causal_conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
-                     slots: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, status: torch.Tensor,
-                     write_state: bool = True) -> torch.Tensor:
-    """silu(conv(x) + bias) per channel over each row's new tokens; ``x`` [T, >= channels] (rows may be
+                     slots: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, token_row: torch.Tensor,
+                     status: torch.Tensor, write_state: bool = True) -> torch.Tensor:
+    """silu(conv(x) + bias) per channel over each row's new tokens (``token_row``: the row of every token); ``x`` [T, >= channels] (rows may be
     strided), ``w`` float32 [channels, taps] whose last column weighs the current token.  ``state``
     [slots, (taps - 1) * channels] float32 (rows may be strided) holds every request's last taps - 1
     inputs, oldest first, and is brought up to date."""
-    _cuda(x, w, bias, state, slots, row_q_start, row_q_len, status)
-    _i32(slots, row_q_start, row_q_len)
-    _require(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= channels and x.dtype in DTYPE_CODE, "x shape")
+    _cuda(x, w, bias, state, slots, row_q_start, row_q_len, token_row, status)
+    _i32(slots, row_q_start, row_q_len, token_row)
+    _require(x.dim() == 2 and x.stride(1) == 1 and x.shape[1] >= channels and x.dtype in DTYPE_CODE
+             and token_row.numel() == x.shape[0], "x shape")
     _require(w.dim() == 2 and w.shape[0] == channels and w.dtype == torch.float32 and w.is_contiguous(), "w must be float32 [channels, taps]")
     taps = w.shape[1]
     _f32_vector(bias, channels, "the bias")
@@ -427,8 +429,9 @@ def causal_conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torc
     out = torch.empty((x.shape[0], channels), dtype=x.dtype, device=x.device)
     _check(library().zb_causal_conv_silu(
         _ptr(out), _ptr(x), x.stride(0), _ptr(state), state.stride(0), _ptr(slots), _ptr(row_q_start), _ptr(row_q_len),
-        slots.numel(), _ptr(w), _ptr(bias), 0, channels, taps, state.shape[0], int(write_state), DTYPE_CODE[x.dtype],
-        _ptr(status), _stream()), "causal_conv_silu")
+        _ptr(token_row), x.shape[0], slots.numel(), _ptr(w), _ptr(bias), 0, channels, taps, state.shape[0],
+        int(write_state), DTYPE_CODE[x.dtype], _ptr(status), _stream()), "causal_conv_silu",
+        kernels=2 if write_state and taps > 1 else 1)
     return out
 
 
@@ -447,7 +450,7 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     to ``state`` [slots, heads * key_dim * value_dim] float32 (rows may be strided); returns o as float32
     [T, heads * value_dim].  q, k, v: [T, .] with unit inner stride, head h at column h * width.
     ``mode`` "gated": a = sigmoid(decay_logits + decay_bias)^inv_tau per key channel (logits float32
-    [T, heads * key_dim]), q times ``q_scale``.  ``mode`` "state_space": step = softplus(dt + dt_bias),
+    [T, heads * key_dim], overwritten with the decays), q times ``q_scale``.  ``mode`` "state_space": step = softplus(dt + dt_bias),
     a = exp(-exp(a_log) step) per head, k times step, o += skip * v; q and k belong to the head's group
     (head // heads_per_group at column group * key_dim)."""
     _cuda(q, k, v, state, slots, row_q_start, row_q_len, status, decay_logits, decay_bias, dt, dt_bias, a_log, skip)
@@ -476,9 +479,9 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
         _ptr(out), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(decay_logits),
         decay_logits.stride(0) if gated else 0, _ptr(decay_bias), _ptr(dt), dt.stride(0) if not gated else 0,
         _ptr(dt_bias), _ptr(a_log), _ptr(skip), 0, _ptr(state), state.stride(0), _ptr(slots), _ptr(row_q_start),
-        _ptr(row_q_len), slots.numel(), heads, key_dim, value_dim, int(heads_per_group), state.shape[0],
+        _ptr(row_q_len), slots.numel(), T, heads, key_dim, value_dim, int(heads_per_group), state.shape[0],
         int(write_state), float(q_scale), float(inv_tau), 0 if gated else 1, DTYPE_CODE[v.dtype], _ptr(status),
-        _stream()), "decayed_state_scan")
+        _stream()), "decayed_state_scan", kernels=2 if gated else 1)
     return out
 
 

@@ -7,6 +7,10 @@
     python -m zephyr_b200.kernels.timing sample --rows 8 --vocab 151936
     python -m zephyr_b200.kernels.timing products --tokens 2048 --hidden 1024 --ffn 3072
     python -m zephyr_b200.kernels.timing gemm_tc --tokens 2048 --n 6144 --k 1024 [--swiglu] [--library]
+    python -m zephyr_b200.kernels.timing state_scan --mode gated|state_space --heads 8 --head-dim 128 --value-dim 256 [--tokens 0 --rows 8]
+    python -m zephyr_b200.kernels.timing conv_silu --n 2560 [--tokens 0 --rows 8]
+    python -m zephyr_b200.kernels.timing norms --hidden 2048 --n 2048
+    python -m zephyr_b200.kernels.timing decode_attention --context 1024 --chunk 1024
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
 that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
@@ -83,10 +87,12 @@ def decode_attention(args) -> dict:
     row_ctx = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
     status, out = ops.new_status(device), torch.empty_like(q)
     split = args.split or None
+    chunk = getattr(args, "chunk", 0)
+    masks = dict(chunk=chunk, sinks=torch.zeros(nh, device=device)) if chunk else {}
 
     def run(i):
         ops.paged_decode(q, caches[i % len(caches)], table, rows, rows, row_ctx, ctx, nh, nkv, hd, args.window,
-                         1 / math.sqrt(hd), status, out=out, split_size=split)
+                         1 / math.sqrt(hd), status, out=out, split_size=split, **masks)
     us = _time(run, args.warmup, args.iters)
     trace = torch.zeros((1024, 8), dtype=torch.int32, device=device)
     ops.paged_decode_trace(trace)
@@ -95,9 +101,11 @@ def decode_attention(args) -> dict:
     ops.paged_decode_trace(None)
     ops.check_status(status, "decode_attention")
     live = min(ctx, args.window) if args.window else ctx
+    if chunk:
+        live = min(live, (ctx - 1) % chunk + 1)
     read = B * live * nkv * hd * 2 * 2
     return {"kernel": "paged_decode_kernel", "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
-            "page_size": args.page_size, "window": args.window, "split_size": split or "balanced", "us": round(us, 2),
+            "page_size": args.page_size, "window": args.window, "chunk": chunk, "split_size": split or "balanced", "us": round(us, 2),
             "bytes_read": read, "gbs": round(read / us / 1e3, 1), "timeline_ns": _decode_timeline(trace)}
 
 
@@ -132,10 +140,12 @@ def prefill_attention(args) -> dict:
     zero = torch.zeros(1, dtype=torch.int32, device=device)
     q_len = torch.full((1,), T, dtype=torch.int32, device=device)
     status, out = ops.new_status(device), torch.empty_like(q)
+    chunk = getattr(args, "chunk", 0)
+    masks = dict(chunk=chunk, sinks=torch.zeros(nh, device=device)) if chunk else {}
 
     def run(i):
         ops.paged_prefill(q, caches[i % len(caches)], table, tile_row, tile_q0, zero, q_len, zero, nh, nkv, hd,
-                          args.window, 1 / math.sqrt(hd), status, out=out)
+                          args.window, 1 / math.sqrt(hd), status, out=out, **masks)
     us = _time(run, args.warmup, args.iters)
     trace = torch.zeros((2, 64, 4), dtype=torch.int32, device=device)
     ops.paged_prefill_trace(trace)
@@ -144,9 +154,9 @@ def prefill_attention(args) -> dict:
     ops.paged_prefill_trace(None)
     ops.check_status(status, "prefill_attention")
     # Two products of 2 * hd flops per (query, visible key) pair and head.
-    pairs = sum(min(t + 1, args.window) if args.window else t + 1 for t in range(T))
+    pairs = sum(min(t + 1, args.window) if args.window else (t % chunk + 1 if chunk else t + 1) for t in range(T))
     flops = 4 * hd * pairs * nh
-    return {"kernel": "paged_prefill_kernel", "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+    return {"kernel": "paged_prefill_kernel", "chunk": chunk, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "page_size": args.page_size, "window": args.window, "us": round(us, 2), "flops": flops,
             "tflops": round(flops / us / 1e6, 1), "longest_cta_ns": _prefill_timeline(trace)}
 
@@ -306,6 +316,122 @@ CASES = {"gemm_tc": gemm_tc, "fused_chain": fused_chain, "products": products, "
          "sample": sample}
 
 
+# ---- the kernels of recurrent layers and of layer norms (csrc/recurrent.cu, csrc/qkv_pairs.cu) ----
+def _row_shape(args, device):
+    """(tokens, slots, row starts, row lengths): ``--rows`` requests of one token each, or one of ``--tokens``."""
+    if args.tokens > 0:
+        counts = [args.tokens]
+    else:
+        counts = [1] * args.rows
+    starts = torch.tensor([sum(counts[:i]) for i in range(len(counts))], dtype=torch.int32, device=device)
+    return sum(counts), torch.arange(len(counts), dtype=torch.int32, device=device), starts, \
+        torch.tensor(counts, dtype=torch.int32, device=device)
+
+
+def state_scan(args) -> dict:
+    """The decayed outer-product recurrence: ``--mode gated|state_space``, ``--heads``, ``--head-dim`` key
+    channels, ``--value-dim`` value channels; ``--tokens 0`` decodes ``--rows`` requests by one token."""
+    device = torch.device("cuda")
+    H, D, V = args.heads, args.head_dim, args.value_dim
+    T, slots, starts, lens = _row_shape(args, device)
+    R = slots.numel()
+    state_bytes = R * H * D * V * 4
+    states = [torch.zeros((R, H * D * V), device=device) for _ in range(_copies(state_bytes) if args.tokens == 0 else 1)]
+    bf = torch.bfloat16
+    status = ops.new_status(device)
+    if args.mode == "gated":
+        q, k, v = (torch.randn((T, H * n), device=device, dtype=bf) for n in (D, D, V))
+        z, bias = torch.randn((T, H * D), device=device) + 3.0, torch.zeros(H * D, device=device)
+
+        def run(i):
+            ops.decayed_state_scan("gated", q, k, v, H, D, V, states[i % len(states)], slots, starts, lens, status,
+                                   decay_logits=z, decay_bias=bias, inv_tau=1 / 16, q_scale=D ** -0.5)
+        read = T * (2 * H * D * 2 + H * V * 2 + H * D * 4)
+    else:
+        G = max(1, args.kv_heads)
+        q, k = (torch.randn((T, G * D), device=device, dtype=bf) for _ in range(2))
+        v, dt = torch.randn((T, H * V), device=device, dtype=bf), torch.randn((T, H), device=device, dtype=bf)
+        consts = [torch.zeros(H, device=device) for _ in range(3)]
+
+        def run(i):
+            ops.decayed_state_scan("state_space", q, k, v, H, D, V, states[i % len(states)], slots, starts, lens, status,
+                                   dt=dt, dt_bias=consts[0], a_log=consts[1], skip=consts[2], heads_per_group=H // G)
+        read = T * (2 * G * D * 2 + H * V * 2 + H * 2)
+    us = _time(run, args.warmup, args.iters)
+    ops.check_status(status, "state_scan")
+    moved = 2 * state_bytes + read + T * H * V * 4
+    flops = 4 * T * H * D * V          # two multiply-adds per state element and token
+    return {"kernel": "decayed_state_scan_kernel", "mode": args.mode, "rows": R, "tokens": T, "heads": H, "key_dim": D,
+            "value_dim": V, "us": round(us, 2), "bytes": moved, "gbs": round(moved / us / 1e3, 1),
+            "tflops_fp32": round(flops / us / 1e6, 2)}
+
+
+def conv_silu(args) -> dict:
+    device = torch.device("cuda")
+    C, taps = args.n, 4
+    T, slots, starts, lens = _row_shape(args, device)
+    xs = [torch.randn((T, C), device=device, dtype=torch.bfloat16) for _ in range(_copies(T * C * 2))]
+    w, b = torch.randn((C, taps), device=device), torch.zeros(C, device=device)
+    state = torch.zeros((slots.numel(), (taps - 1) * C), device=device)
+    status = ops.new_status(device)
+    token_row = torch.repeat_interleave(torch.arange(slots.numel(), device=device), lens.long()).int()
+    us = _time(lambda i: ops.causal_conv_silu(xs[i % len(xs)], C, w, b, state, slots, starts, lens, token_row, status),
+               args.warmup, args.iters)
+    moved = T * C * 4 + 2 * state.numel() * 4
+    return {"kernel": "causal_conv_silu_kernel", "tokens": T, "rows": slots.numel(), "channels": C, "us": round(us, 2),
+            "bytes": moved, "gbs": round(moved / us / 1e3, 1)}
+
+
+def norms(args) -> dict:
+    """The fused residual sum + layer norm + next layer norm beside the other architecture's residual sum +
+    RMS norm, the gated group norm, and the two kernels between a q/k/v projection and the attention."""
+    device = torch.device("cuda")
+    T, H = (args.tokens or args.rows), args.hidden
+    bf = torch.bfloat16
+    n = _copies(T * H * 12)
+    residual32 = [torch.randn((T, H), device=device) for _ in range(n)]
+    residual16 = [torch.randn((T, H), device=device, dtype=bf) for _ in range(n)]
+    delta = [torch.randn((T, H), device=device, dtype=bf) for _ in range(n)]
+    w = [torch.ones(H, device=device) for _ in range(4)]
+    out = {"tokens": T, "hidden": H}
+    us = _time(lambda i: ops.residual_layer_norm(residual32[i % n], delta[i % n], w[0], w[1], 1e-6, 0.5, w[2], w[3], 1e-6),
+               args.warmup, args.iters)
+    out["residual_layer_norm"] = {"us": round(us, 2), "gbs": round(T * H * 12 / us / 1e3, 1)}
+    us = _time(lambda i: ops.add_rmsnorm(residual16[i % n], delta[i % n], w[0], 1e-6), args.warmup, args.iters)
+    out["add_rmsnorm"] = {"us": round(us, 2), "gbs": round(T * H * 8 / us / 1e3, 1)}
+    W = args.n
+    o = [torch.randn((T, W), device=device) for _ in range(_copies(T * W * 8))]
+    gate = torch.randn((T, W), device=device, dtype=bf)
+    scale = torch.ones(W, device=device)
+    us = _time(lambda i: ops.gated_group_rms_norm(o[i % len(o)], gate, scale, W // 2, 1e-6, True), args.warmup, args.iters)
+    out["gated_group_rms_norm"] = {"width": W, "us": round(us, 2), "gbs": round(T * W * 8 / us / 1e3, 1)}
+    nh, nkv, hd = args.heads, args.kv_heads, args.head_dim
+    width = (nh + 2 * nkv) * hd
+    pages = math.ceil(T / args.page_size) + 1
+    cache = torch.zeros((pages, 2, nkv, args.page_size, hd), device=device, dtype=bf)
+    table = torch.arange(1, pages, dtype=torch.int32, device=device).view(1, -1)
+    positions = torch.arange(T, dtype=torch.int32, device=device)
+    token_row = torch.zeros(T, dtype=torch.int32, device=device)
+    status = ops.new_status(device)
+    qkv32 = [torch.randn((T, width), device=device) for _ in range(_copies(T * width * 6))]
+    qkv16 = [t.to(bf) for t in qkv32]
+    ones, freqs = torch.ones(hd, device=device), torch.rand(hd // 2, device=device)
+    bias = torch.zeros(width, device=device)
+    us = _time(lambda i: ops.qkv_pairs(qkv32[i % len(qkv32)], nh, nkv, hd, hd, bias, ones, ones, 1e-6, freqs, hd, positions,
+                                       token_row, cache, table, status, bf), args.warmup, args.iters)
+    out["qkv_pairs"] = {"width": width, "us": round(us, 2), "gbs": round(T * width * 6 / us / 1e3, 1)}
+    cos, sin = torch.ones((T, hd // 2), device=device), torch.zeros((T, hd // 2), device=device)
+    ones16 = ones.to(bf)
+    us = _time(lambda i: ops.qk_norm_rope_cache(qkv16[i % len(qkv16)], nh, nkv, hd, ones16, ones16, 1e-6, cos, sin, positions,
+                                                token_row, cache, table, status), args.warmup, args.iters)
+    out["qk_norm_rope_cache"] = {"width": width, "us": round(us, 2), "gbs": round(T * width * 4 / us / 1e3, 1)}
+    ops.check_status(status, "norms")
+    return out
+
+
+CASES.update({"state_scan": state_scan, "conv_silu": conv_silu, "norms": norms})
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m zephyr_b200.kernels.timing", description=__doc__.split("\n")[0])
     parser.add_argument("case", choices=sorted(CASES))
@@ -319,6 +445,9 @@ def main(argv=None) -> int:
     parser.add_argument("--head-dim", type=int, default=128)
     parser.add_argument("--page-size", type=int, default=16)
     parser.add_argument("--window", type=int, default=0)
+    parser.add_argument("--chunk", type=int, default=0, help="attention: a chunked mask of this size, with sinks")
+    parser.add_argument("--value-dim", type=int, default=128, help="state_scan: value channels per head")
+    parser.add_argument("--mode", choices=("gated", "state_space"), default="gated")
     parser.add_argument("--split", type=int, default=0, help="fixed splits of this many positions in the decode kernel (0: balanced items)")
     parser.add_argument("--rows", type=int, default=8)
     parser.add_argument("--n", type=int, default=6144)

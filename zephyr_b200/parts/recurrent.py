@@ -43,7 +43,7 @@ from ..kernels import ops
 from ..weights.loader import ROLE_LINEAR, ROLE_NORM, ROLE_ZERO, WeightDecl
 from .base import MIXERS, Mixer, StepContext, lookup, register_mixer
 
-MAX_KEY_CHANNELS = 256        # what the scan kernel takes per head (csrc/recurrent.cu: 8 warps of 32 channels)
+MAX_KEY_CHANNELS = 256        # what the scan kernel takes per head (csrc/recurrent.cu: 16 warps of 16 channels)
 
 
 def _vector(weights: Mapping[str, torch.Tensor], name: str) -> torch.Tensor:
@@ -176,7 +176,7 @@ class Mamba2(Mixer):
         projected = ops.linear(x, self.w_in)             # z | x | B | C | dt
         mixed = ops.causal_conv_silu(projected[:, inner:], self.channels, self.conv_w, self.conv_b,
                                      store[:, self.scan_floats:], ctx.state_slots, ctx.row_q_start, ctx.row_q_len,
-                                     ctx.status, write_state=call.writes_cache)
+                                     ctx.token_row, ctx.status, write_state=call.writes_cache)
         o = ops.decayed_state_scan("state_space", mixed[:, inner + gn:], mixed[:, inner:inner + gn], mixed[:, :inner],
                                    self.heads, self.state, self.vdim, store[:, :self.scan_floats], ctx.state_slots,
                                    ctx.row_q_start, ctx.row_q_len, ctx.status, dt=projected[:, inner + self.channels:],
