@@ -112,3 +112,22 @@ def test_chunked_groups_give_pages_back_at_chunk_edges():
     manager.free_request("a")
     manager.check_invariants()
     assert manager.num_free_pages(0) == manager.num_free_pages(1) == 11
+
+
+def test_random_model_from_the_command_line(tmp_path):
+    """``random-model`` writes a Legelix folder whose decay projection has the inner size asked for, and
+    the folder reads back as the same configuration with every declared tensor present."""
+    from zephyr_b200.cli import main
+    from zephyr_b200.config import load_model_config
+    from zephyr_b200.parts import expected_weights
+    from zephyr_b200.weights import Checkpoint
+    from zephyr_b200.weights.loader import check_store
+
+    source = tmp_path / "config.json"
+    source.write_text(json.dumps(CONFIGS["P"]))
+    assert main(["random-model", "--config", str(source), "--out", str(tmp_path / "model"), "--decay-rank", "6", "--seed", "3"]) == 0
+    config = load_model_config(tmp_path / "model")
+    assert config.to_dict() == CONFIGS["P"]
+    store = Checkpoint(tmp_path / "model")
+    check_store(store, expected_weights(config.to_model_spec()))
+    assert tuple(store.shape("l0.mix.a1")) == (6, 64) and tuple(store.shape("l0.mix.a2")) == (32, 6)

@@ -35,7 +35,7 @@ def _ids(value: str) -> list[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(prog="zephyr_b200", description="Qwen3 inference engine for one B200")
+    parser = argparse.ArgumentParser(prog="zephyr_b200", description="LLM inference engine for one B200")
     commands = parser.add_subparsers(dest="command", required=True)
 
     gen = commands.add_parser("generate", help="Generate from prompts given as token ids")
@@ -72,6 +72,9 @@ def build_parser() -> argparse.ArgumentParser:
     rand.add_argument("--seed", type=int, default=0)
     rand.add_argument("--out", type=Path, required=True)
     rand.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
+    rand.add_argument("--decay-rank", type=_positive_int, default=16,
+                      help="Legelix: the inner size of the decay projection of its gated linear attention, which a "
+                           "checkpoint's tensors give and no configuration key names")
     return parser
 
 
@@ -138,6 +141,8 @@ def _random_model(args, parser) -> int:
     try:
         data = json.loads(args.config.read_text())
         config = resolve_architecture(data, str(args.config)).config_class.from_dict(data, str(args.config))
+        if getattr(config, "decay_rank", 0) is None:
+            config.decay_rank = args.decay_rank
         folder = write_random_model(config, args.seed, args.out, dtype=getattr(torch, args.dtype))
     except (ZephyrError, OSError, ValueError) as error:
         print(f"zephyr_b200: {type(error).__name__}: {error}", file=sys.stderr)

@@ -34,8 +34,25 @@ struct QkvPairsArgs {
   const int* block_table;
   int max_blocks, page_size, num_pages, num_rows;
   int nh, nkv, kd, vd;
+  int pairs_aligned;         // every pair of the projection, the bias and the scales may move as one 8-byte value
   int* status;
 };
+
+__device__ __forceinline__ void load_pair(const float* p, bool aligned, float& a, float& b) {
+  if (aligned) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    a = v.x; b = v.y;
+  } else {
+    a = p[0]; b = p[1];
+  }
+}
+__device__ __forceinline__ void load_pair(const __nv_bfloat16* p, bool aligned, float& a, float& b) {
+  a = __bfloat162float(p[0]); b = __bfloat162float(p[1]);
+}
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
 
 template <typename IN, typename T>
 __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairsArgs a) {
@@ -58,10 +75,17 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairs
   for (int k = 0; k < QP_PAIRS; ++k) {
     const int i = 2 * (lane + 32 * k);
     x[k][0] = x[k][1] = 0.0f;
-    if (i < dim) {
-      x[k][0] = to_float(src[i]) + (a.bias != nullptr ? a.bias[col + i] : 0.0f);
-      if (i + 1 < dim) x[k][1] = to_float(src[i + 1]) + (a.bias != nullptr ? a.bias[col + i + 1] : 0.0f);
+    if (i + 1 < dim) {
+      load_pair(src + i, a.pairs_aligned != 0, x[k][0], x[k][1]);
+      if (a.bias != nullptr) {
+        float b0, b1;
+        load_pair(a.bias + col + i, a.pairs_aligned != 0, b0, b1);
+        x[k][0] += b0; x[k][1] += b1;
+      }
       ss += x[k][0] * x[k][0] + x[k][1] * x[k][1];
+    } else if (i < dim) {
+      x[k][0] = to_float(src[i]) + (a.bias != nullptr ? a.bias[col + i] : 0.0f);
+      ss += x[k][0] * x[k][0];
     }
   }
   {
@@ -71,9 +95,13 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairs
 #pragma unroll
       for (int k = 0; k < QP_PAIRS; ++k) {
         const int i = 2 * (lane + 32 * k);
-        if (i < dim) {
+        if (i + 1 < dim) {
+          float w0, w1;
+          load_pair(w + i, a.pairs_aligned != 0, w0, w1);
+          x[k][0] = x[k][0] * inv * w0;
+          x[k][1] = x[k][1] * inv * w1;
+        } else if (i < dim) {
           x[k][0] = x[k][0] * inv * w[i];
-          if (i + 1 < dim) x[k][1] = x[k][1] * inv * w[i + 1];
         }
       }
     }
@@ -119,8 +147,12 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairs
     const int i = 2 * (lane + 32 * k);
     if (i < dim) {
       const int at = swizzle_pos >= 0 ? kv_element_index(i, swizzle_pos, dim, sizeof(T)) : i;
-      dst[at] = from_float<T>(x[k][0]);
-      if (i + 1 < dim) dst[at + 1] = from_float<T>(x[k][1]);     // a pair never straddles a 16-byte chunk
+      if (i + 1 < dim && a.pairs_aligned) {
+        store_pair(dst + at, x[k][0], x[k][1]);                    // a pair never straddles a 16-byte chunk
+      } else {
+        dst[at] = from_float<T>(x[k][0]);
+        if (i + 1 < dim) dst[at + 1] = from_float<T>(x[k][1]);
+      }
     }
   }
 }
@@ -145,6 +177,9 @@ ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const fl
   a.token_row = token_row; a.cache = cache; a.block_table = block_table; a.max_blocks = max_blocks;
   a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows; a.nh = nh; a.nkv = nkv; a.kd = kd;
   a.vd = vd; a.status = status;
+  auto even = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 8 == 0; };
+  a.pairs_aligned = kd % 2 == 0 && vd % 2 == 0 && stride % 2 == 0 && even(qkv) && even(bias) && even(q_norm_w) &&
+                    even(k_norm_w) && even(q_out) && even(cache);
   const int heads = cache != nullptr ? nh + 2 * nkv : nh;
   const dim3 grid(tokens, (heads + QP_WARPS - 1) / QP_WARPS);
   auto s = static_cast<cudaStream_t>(stream);

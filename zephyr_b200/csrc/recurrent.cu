@@ -15,6 +15,7 @@
 // the state, the sums.  A row's tokens are run in their order, so a result does not depend on how a
 // prompt was cut into steps or on what else a step carries.
 #include <algorithm>
+#include <initializer_list>
 
 #include "common.cuh"
 
@@ -76,6 +77,113 @@ __global__ void residual_layer_norm_kernel(float* residual, const T* delta, cons
   layer_norm_stats(ln_row, H, eps2, scratch, mean, rstd);
   for (int i = threadIdx.x; i < H; i += blockDim.x)
     out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w2, w_dtype, i), load_scale(b2, w_dtype, i)));
+}
+
+// The same two kernels for rows of up to LN_VEC_MAX elements whose length is a multiple of four: a thread
+// keeps its share of the row in registers as vectors of four, loads and stores move 8 or 16 bytes, and
+// nothing passes through shared memory but the two sums.
+constexpr int LN_VEC_THREADS = 256;
+constexpr int LN_VEC_ITEMS = 8;
+constexpr int LN_VEC_MAX = LN_VEC_THREADS * LN_VEC_ITEMS * 4;
+
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+__device__ __forceinline__ void vec_stats(const float4 (&r)[LN_VEC_ITEMS], int nv, int H, float eps, float* scratch,
+                                          float& mean, float& rstd) {
+  float s = 0.0f;
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j)
+    if (static_cast<int>(threadIdx.x) + j * LN_VEC_THREADS < nv) s += (r[j].x + r[j].y) + (r[j].z + r[j].w);
+  mean = block_sum(s, scratch) / static_cast<float>(H);
+  float v = 0.0f;
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j)
+    if (static_cast<int>(threadIdx.x) + j * LN_VEC_THREADS < nv) {
+      const float a = r[j].x - mean, b = r[j].y - mean, c = r[j].z - mean, d = r[j].w - mean;
+      v += (a * a + b * b) + (c * c + d * d);
+    }
+  rstd = 1.0f / sqrtf(block_sum(v, scratch) / static_cast<float>(H) + eps);
+}
+
+__device__ __forceinline__ float4 vec_affine(float4 x, float mean, float rstd, const float* w, const float* b, int at) {
+  const float4 wv = load4(w + at), bv = load4(b + at);
+  return make_float4(fmaf((x.x - mean) * rstd, wv.x, bv.x), fmaf((x.y - mean) * rstd, wv.y, bv.y),
+                     fmaf((x.z - mean) * rstd, wv.z, bv.z), fmaf((x.w - mean) * rstd, wv.w, bv.w));
+}
+
+template <typename X, typename T>
+__global__ void __launch_bounds__(LN_VEC_THREADS)
+layer_norm_vec_kernel(T* out, const X* x, const float* w, const float* b, float eps, int H) {
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * H;
+  const int nv = H / 4;
+  float4 r[LN_VEC_ITEMS];
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j) {
+    const int i = threadIdx.x + j * LN_VEC_THREADS;
+    if (i < nv) r[j] = load4(x + base + 4 * i);
+  }
+  float mean, rstd;
+  vec_stats(r, nv, H, eps, scratch, mean, rstd);
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j) {
+    const int i = threadIdx.x + j * LN_VEC_THREADS;
+    if (i < nv) store4(out + base + 4 * i, vec_affine(r[j], mean, rstd, w, b, 4 * i));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LN_VEC_THREADS)
+residual_layer_norm_vec_kernel(float* residual, const T* delta, const float* w1, const float* b1, float mult, T* out,
+                               const float* w2, const float* b2, float eps1, float eps2, int H) {
+  __shared__ float scratch[33];
+  const size_t base = static_cast<size_t>(blockIdx.x) * H;
+  const int nv = H / 4;
+  float4 r[LN_VEC_ITEMS];
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j) {
+    const int i = threadIdx.x + j * LN_VEC_THREADS;
+    if (i < nv) r[j] = load4(delta + base + 4 * i);
+  }
+  float mean, rstd;
+  vec_stats(r, nv, H, eps1, scratch, mean, rstd);
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j) {
+    const int i = threadIdx.x + j * LN_VEC_THREADS;
+    if (i < nv) {
+      const float4 y = vec_affine(r[j], mean, rstd, w1, b1, 4 * i), old = load4(residual + base + 4 * i);
+      r[j] = make_float4(fmaf(mult, y.x, old.x), fmaf(mult, y.y, old.y), fmaf(mult, y.z, old.z), fmaf(mult, y.w, old.w));
+      store4(residual + base + 4 * i, r[j]);
+    }
+  }
+  if (out == nullptr) return;
+  vec_stats(r, nv, H, eps2, scratch, mean, rstd);
+#pragma unroll
+  for (int j = 0; j < LN_VEC_ITEMS; ++j) {
+    const int i = threadIdx.x + j * LN_VEC_THREADS;
+    if (i < nv) store4(out + base + 4 * i, vec_affine(r[j], mean, rstd, w2, b2, 4 * i));
+  }
+}
+
+// True if rows of H elements and these pointers take the vector kernels (float32 scales).
+inline bool ln_vectors(int H, int w_dtype, std::initializer_list<const void*> pointers) {
+  if (H % 4 != 0 || H > LN_VEC_MAX || w_dtype != DTYPE_F32) return false;
+  for (const void* p : pointers)
+    if (p != nullptr && reinterpret_cast<uintptr_t>(p) % 16 != 0) return false;
+  return true;
 }
 
 template <typename T>
@@ -391,6 +499,54 @@ __global__ void gated_group_rms_norm_kernel(T* out, const float* o, const T* gat
   }
 }
 
+// The same for groups of up to GN_VEC_MAX columns that are a multiple of four, with aligned rows: a lane
+// keeps its share of the group in registers, so that o and the gate are read once.
+constexpr int GN_VEC_ITEMS = 16;
+constexpr int GN_VEC_MAX = 32 * GN_VEC_ITEMS * 4;
+
+template <typename T>
+__global__ void __launch_bounds__(128) gated_group_rms_norm_vec_kernel(T* out, const float* o, const T* gate, long long gate_stride,
+                                                const float* w, int w_len, int width, int group, float eps,
+                                                int gate_first, int tokens) {
+  const int groups = width / group;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(tokens) * groups) return;
+  const int lane = threadIdx.x & 31, nv = group / 4;
+  const long long t = item / groups;
+  const int c0 = static_cast<int>(item - t * groups) * group;
+  // With the gate first only the product is kept; with the gate last, the unit-norm values, and the gate
+  // is read again (a second time from the cache) when they are scaled.
+  float4 val[GN_VEC_ITEMS];
+  float ss = 0.0f;
+#pragma unroll
+  for (int j = 0; j < GN_VEC_ITEMS; ++j) {
+    const int i = lane + 32 * j;
+    if (i < nv) {
+      val[j] = load4(o + t * width + c0 + 4 * i);
+      if (gate_first) {
+        const float4 raw = load4(gate + t * gate_stride + c0 + 4 * i);
+        val[j] = make_float4(val[j].x * silu_f(raw.x), val[j].y * silu_f(raw.y), val[j].z * silu_f(raw.z),
+                             val[j].w * silu_f(raw.w));
+      }
+      ss += (val[j].x * val[j].x + val[j].y * val[j].y) + (val[j].z * val[j].z + val[j].w * val[j].w);
+    }
+  }
+  const float r = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(group) + eps);
+#pragma unroll
+  for (int j = 0; j < GN_VEC_ITEMS; ++j) {
+    const int i = lane + 32 * j;
+    if (i < nv) {
+      const float4 wv = load4(w + (c0 + 4 * i) % w_len);
+      float4 y = make_float4(val[j].x * r * wv.x, val[j].y * r * wv.y, val[j].z * r * wv.z, val[j].w * r * wv.w);
+      if (!gate_first) {
+        const float4 raw = load4(gate + t * gate_stride + c0 + 4 * i);
+        y = make_float4(y.x * silu_f(raw.x), y.y * silu_f(raw.y), y.z * silu_f(raw.z), y.w * silu_f(raw.w));
+      }
+      store4(out + t * width + c0 + 4 * i, y);
+    }
+  }
+}
+
 // out = sa * a + sb * b, float32 arithmetic, one rounding; a and b may be float32 whatever out is.
 template <typename IN, typename T>
 __global__ void scaled_sum_kernel(T* out, const IN* a, const IN* b, float sa, float sb, long long n) {
@@ -419,6 +575,20 @@ ZB_API int zb_layer_norm(void* out, const void* x, const void* w, const void* b,
   if (rows < 0 || H <= 0) return ERR_BAD_ARGUMENT;
   if (rows == 0) return OK;
   auto s = static_cast<cudaStream_t>(stream);
+  if (ln_vectors(H, w_dtype, {out, x, w, b})) {
+    const float* wf = static_cast<const float*>(w);
+    const float* bf = static_cast<const float*>(b);
+    using bf16 = __nv_bfloat16;
+    if (x_dtype == DTYPE_F32 && out_dtype == DTYPE_F32)
+      layer_norm_vec_kernel<float, float><<<rows, LN_VEC_THREADS, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(x), wf, bf, eps, H);
+    else if (x_dtype == DTYPE_F32)
+      layer_norm_vec_kernel<float, bf16><<<rows, LN_VEC_THREADS, 0, s>>>(static_cast<bf16*>(out), static_cast<const float*>(x), wf, bf, eps, H);
+    else if (out_dtype == DTYPE_F32)
+      layer_norm_vec_kernel<bf16, float><<<rows, LN_VEC_THREADS, 0, s>>>(static_cast<float*>(out), static_cast<const bf16*>(x), wf, bf, eps, H);
+    else
+      layer_norm_vec_kernel<bf16, bf16><<<rows, LN_VEC_THREADS, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(x), wf, bf, eps, H);
+    return launch_result();
+  }
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   const int threads = norm_threads(H);
 #define ZB_LN(X, T)                                                                                    \
@@ -441,6 +611,20 @@ ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void
   if (rows < 0 || H <= 0) return ERR_BAD_ARGUMENT;
   if (rows == 0) return OK;
   auto s = static_cast<cudaStream_t>(stream);
+  if (ln_vectors(H, w_dtype, {residual, delta, out, w1, b1, w2, b2})) {
+    const float* f1 = static_cast<const float*>(w1);
+    const float* g1 = static_cast<const float*>(b1);
+    const float* f2 = static_cast<const float*>(w2);
+    const float* g2 = static_cast<const float*>(b2);
+    if (dtype == DTYPE_F32)
+      residual_layer_norm_vec_kernel<float><<<rows, LN_VEC_THREADS, 0, s>>>(
+          residual, static_cast<const float*>(delta), f1, g1, mult, static_cast<float*>(out), f2, g2, eps1, eps2, H);
+    else
+      residual_layer_norm_vec_kernel<__nv_bfloat16><<<rows, LN_VEC_THREADS, 0, s>>>(
+          residual, static_cast<const __nv_bfloat16*>(delta), f1, g1, mult, static_cast<__nv_bfloat16*>(out), f2, g2,
+          eps1, eps2, H);
+    return launch_result();
+  }
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   const int threads = norm_threads(H);
   if (dtype == DTYPE_F32) {
@@ -551,6 +735,21 @@ ZB_API int zb_gated_group_rms_norm(void* out, const float* o, const void* gate, 
   const int warps = 4;
   const unsigned blocks = static_cast<unsigned>((items + warps - 1) / warps);
   auto s = static_cast<cudaStream_t>(stream);
+  const int elem = dtype == DTYPE_F32 ? 4 : 2;
+  if (group % 4 == 0 && group <= GN_VEC_MAX && w_len % 4 == 0 && w_dtype == DTYPE_F32 && (gate_stride * elem) % (4 * elem) == 0 &&
+      reinterpret_cast<uintptr_t>(gate) % (4 * elem) == 0 && reinterpret_cast<uintptr_t>(o) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(out) % (4 * elem) == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0) {
+    const float* wf = static_cast<const float*>(w);
+    if (dtype == DTYPE_F32)
+      gated_group_rms_norm_vec_kernel<float><<<blocks, warps * 32, 0, s>>>(
+          static_cast<float*>(out), o, static_cast<const float*>(gate), gate_stride, wf, w_len, width, group, eps,
+          gate_first, tokens);
+    else
+      gated_group_rms_norm_vec_kernel<__nv_bfloat16><<<blocks, warps * 32, 0, s>>>(
+          static_cast<__nv_bfloat16*>(out), o, static_cast<const __nv_bfloat16*>(gate), gate_stride, wf, w_len, width,
+          group, eps, gate_first, tokens);
+    return launch_result();
+  }
   if (dtype == DTYPE_F32)
     gated_group_rms_norm_kernel<float><<<blocks, warps * 32, 0, s>>>(
         static_cast<float*>(out), o, static_cast<const float*>(gate), gate_stride, w, w_dtype, w_len, width, group, eps,
