@@ -226,7 +226,7 @@ constexpr int CONV_TOKENS = 1;
 
 template <typename T>
 __global__ void causal_conv_silu_kernel(const ConvArgs a, const int* token_row, int tokens) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= a.C) return;
   float w[CONV_MAX_TAPS];
 #pragma unroll
@@ -234,7 +234,7 @@ __global__ void causal_conv_silu_kernel(const ConvArgs a, const int* token_row, 
   const float bias = load_scale(a.bias, a.w_dtype, c);
   const T* x = static_cast<const T*>(a.x);
   T* out = static_cast<T*>(a.out);
-  const int first = blockIdx.y * CONV_TOKENS;
+  const int first = blockIdx.x * CONV_TOKENS;
   for (int t = first; t < min(first + CONV_TOKENS, tokens); ++t) {
     const int row = token_row[t];
     const int slot = a.slots[row];
@@ -256,6 +256,56 @@ __global__ void causal_conv_silu_kernel(const ConvArgs a, const int* token_row, 
     }
     out[static_cast<long long>(t) * a.C + c] = from_float<T>(silu_f(acc + bias));
   }
+}
+
+// The same for eight adjacent channels a thread (16-byte loads and stores of bfloat16 rows whose length
+// and stride are multiples of eight): the form that runs wherever the shapes allow it.
+__global__ void causal_conv_silu_vec8_kernel(const ConvArgs a, const int* token_row, int tokens) {
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  const int t = blockIdx.x;
+  if (c >= a.C || t >= tokens) return;
+  const int row = token_row[t];
+  const int slot = a.slots[row];
+  if (slot < 0 || slot >= a.num_slots) {
+    report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+    return;
+  }
+  const int i = t - a.row_q_start[row];
+  const float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
+  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a.x);
+  const float* w = static_cast<const float*>(a.w);
+  float acc[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {            // oldest input first, as the weights lie
+    if (j < a.taps) {
+      const int back = a.taps - 1 - j;
+      float in[8];
+      if (i - back >= 0) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t - back) * a.x_stride + c);
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 f = __bfloat1622float2(pairs[u]);
+          in[2 * u] = f.x; in[2 * u + 1] = f.y;
+        }
+      } else {
+        const float* from = state + static_cast<long long>(a.taps - 1 + i - back) * a.C + c;
+        const float4 lo = *reinterpret_cast<const float4*>(from), hi = *reinterpret_cast<const float4*>(from + 4);
+        in[0] = lo.x; in[1] = lo.y; in[2] = lo.z; in[3] = lo.w; in[4] = hi.x; in[5] = hi.y; in[6] = hi.z; in[7] = hi.w;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc[u] = fmaf(w[(c + u) * a.taps + j], in[u], acc[u]);
+    }
+  }
+  const float* bias = static_cast<const float*>(a.bias);
+  uint4 packed;
+  __nv_bfloat162* outs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+    outs[u] = __floats2bfloat162_rn(silu_f(acc[2 * u] + bias[c + 2 * u]), silu_f(acc[2 * u + 1] + bias[c + 2 * u + 1]));
+  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + static_cast<long long>(t) * a.C + c) = packed;
 }
 
 // After it: every request's last taps - 1 inputs go to its state.  A thread owns a channel of one request.
@@ -668,12 +718,18 @@ ZB_API int zb_causal_conv_silu(void* out, const void* x, long long x_stride, flo
   a.taps = taps; a.num_slots = num_slots; a.write_state = write_state; a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   if (tokens <= 0) return OK;
-  const dim3 grid((C + 127) / 128, (tokens + CONV_TOKENS - 1) / CONV_TOKENS), per_row((C + 127) / 128, rows);
+  const dim3 grid((tokens + CONV_TOKENS - 1) / CONV_TOKENS, (C + 127) / 128), per_row((C + 127) / 128, rows);
   if (dtype == DTYPE_F32) {
     causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>(a, token_row, tokens);
     if (write_state && taps > 1) conv_state_update_kernel<float><<<per_row, 128, 0, s>>>(a);
   } else {
-    causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a, token_row, tokens);
+    const bool vectors = C % 8 == 0 && x_stride % 8 == 0 && slot_stride % 4 == 0 && w_dtype == DTYPE_F32 &&
+                         reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(state) % 16 == 0;
+    if (vectors)
+      causal_conv_silu_vec8_kernel<<<dim3(tokens, (C / 8 + 63) / 64), 64, 0, s>>>(a, token_row, tokens);
+    else
+      causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a, token_row, tokens);
     if (write_state && taps > 1) conv_state_update_kernel<__nv_bfloat16><<<per_row, 128, 0, s>>>(a);
   }
   return launch_result();
