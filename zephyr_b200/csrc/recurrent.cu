@@ -258,54 +258,75 @@ __global__ void causal_conv_silu_kernel(const ConvArgs a, const int* token_row, 
   }
 }
 
-// The same for eight adjacent channels a thread (16-byte loads and stores of bfloat16 rows whose length
-// and stride are multiples of eight): the form that runs wherever the shapes allow it.
-__global__ void causal_conv_silu_vec8_kernel(const ConvArgs a, const int* token_row, int tokens) {
-  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-  const int t = blockIdx.x;
-  if (c >= a.C || t >= tokens) return;
-  const int row = token_row[t];
-  const int slot = a.slots[row];
-  if (slot < 0 || slot >= a.num_slots) {
-    report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
-    return;
+// The form that runs wherever the shapes allow it (bfloat16, an even number of channels, aligned rows):
+// a CTA takes CONV_TILE consecutive tokens of the stream and 128 channels, a thread two adjacent
+// channels, which it walks down the tile with the last inputs in registers: one 4-byte load and one
+// 4-byte store a token.  Where a tile crosses from one request to the next the window starts again
+// from that request's state.  The tile's rows, slots and first tokens are looked up once, into shared
+// memory.
+constexpr int CONV_TILE = 32;
+
+__global__ void __launch_bounds__(64) causal_conv_silu_tile_kernel(const ConvArgs a, const int* token_row, int tokens) {
+  __shared__ int first_s[CONV_TILE], slot_s[CONV_TILE];       // per token: index within its request's new tokens, slot
+  const int t0 = blockIdx.x * CONV_TILE, nt = min(CONV_TILE, tokens - t0);
+  if (threadIdx.x < nt) {
+    const int row = token_row[t0 + threadIdx.x];
+    const int slot = a.slots[row];
+    first_s[threadIdx.x] = t0 + threadIdx.x - a.row_q_start[row];
+    slot_s[threadIdx.x] = slot;
+    if (slot < 0 || slot >= a.num_slots) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
   }
-  const int i = t - a.row_q_start[row];
-  const float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
+  __syncthreads();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 2;
+  if (c >= a.C) return;
+  const int first = CONV_MAX_TAPS - a.taps;
+  const float* wp = static_cast<const float*>(a.w);
+  float w[CONV_MAX_TAPS][2], win[CONV_MAX_TAPS][2];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+    w[j][0] = j >= first ? wp[c * a.taps + (j - first)] : 0.0f;
+    w[j][1] = j >= first ? wp[(c + 1) * a.taps + (j - first)] : 0.0f;
+    win[j][0] = win[j][1] = 0.0f;
+  }
+  const float bias0 = static_cast<const float*>(a.bias)[c], bias1 = static_cast<const float*>(a.bias)[c + 1];
   const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(a.x);
-  const float* w = static_cast<const float*>(a.w);
-  float acc[8];
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(a.out);
+  for (int k = 0; k < nt; ++k) {
+    const int i = first_s[k], slot = slot_s[k];
+    if (slot < 0 || slot >= a.num_slots) continue;
+    if (k == 0 || i == 0) {
+      // The window before this token: inputs i - taps + 1 .. i - 1, from x or, before the request's first
+      // new token, from its state.  win[j + 1] is what win[j] will be after the shift below.
+      const float* state = a.state + static_cast<long long>(slot) * a.slot_stride;
 #pragma unroll
-  for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
-#pragma unroll
-  for (int j = 0; j < CONV_MAX_TAPS; ++j) {            // oldest input first, as the weights lie
-    if (j < a.taps) {
-      const int back = a.taps - 1 - j;
-      float in[8];
-      if (i - back >= 0) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<long long>(t - back) * a.x_stride + c);
-        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float2 f = __bfloat1622float2(pairs[u]);
-          in[2 * u] = f.x; in[2 * u + 1] = f.y;
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        if (j > first) {
+          const int back = CONV_MAX_TAPS - j;          // win[j] holds the input `back` tokens before this one
+          if (i - back >= 0) {
+            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(
+                x + static_cast<long long>(t0 + k - back) * a.x_stride + c));
+            win[j][0] = v.x; win[j][1] = v.y;
+          } else {
+            const float2 v = *reinterpret_cast<const float2*>(state + static_cast<long long>(a.taps - 1 + i - back) * a.C + c);
+            win[j][0] = v.x; win[j][1] = v.y;
+          }
         }
-      } else {
-        const float* from = state + static_cast<long long>(a.taps - 1 + i - back) * a.C + c;
-        const float4 lo = *reinterpret_cast<const float4*>(from), hi = *reinterpret_cast<const float4*>(from + 4);
-        in[0] = lo.x; in[1] = lo.y; in[2] = lo.z; in[3] = lo.w; in[4] = hi.x; in[5] = hi.y; in[6] = hi.z; in[7] = hi.w;
       }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) acc[u] = fmaf(w[(c + u) * a.taps + j], in[u], acc[u]);
     }
-  }
-  const float* bias = static_cast<const float*>(a.bias);
-  uint4 packed;
-  __nv_bfloat162* outs = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-  for (int u = 0; u < 4; ++u)
-    outs[u] = __floats2bfloat162_rn(silu_f(acc[2 * u] + bias[c + 2 * u]), silu_f(acc[2 * u + 1] + bias[c + 2 * u + 1]));
-  *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + static_cast<long long>(t) * a.C + c) = packed;
+    for (int j = 0; j + 1 < CONV_MAX_TAPS; ++j) { win[j][0] = win[j + 1][0]; win[j][1] = win[j + 1][1]; }
+    const float2 now = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(
+        x + static_cast<long long>(t0 + k) * a.x_stride + c));
+    win[CONV_MAX_TAPS - 1][0] = now.x; win[CONV_MAX_TAPS - 1][1] = now.y;
+    float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+      acc0 = fmaf(w[j][0], win[j][0], acc0);
+      acc1 = fmaf(w[j][1], win[j][1], acc1);
+    }
+    *reinterpret_cast<__nv_bfloat162*>(out + static_cast<long long>(t0 + k) * a.C + c) =
+        __floats2bfloat162_rn(silu_f(acc0 + bias0), silu_f(acc1 + bias1));
+  }
 }
 
 // After it: every request's last taps - 1 inputs go to its state.  A thread owns a channel of one request.
@@ -723,11 +744,13 @@ ZB_API int zb_causal_conv_silu(void* out, const void* x, long long x_stride, flo
     causal_conv_silu_kernel<float><<<grid, 128, 0, s>>>(a, token_row, tokens);
     if (write_state && taps > 1) conv_state_update_kernel<float><<<per_row, 128, 0, s>>>(a);
   } else {
-    const bool vectors = C % 8 == 0 && x_stride % 8 == 0 && slot_stride % 4 == 0 && w_dtype == DTYPE_F32 &&
-                         reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0 &&
-                         reinterpret_cast<uintptr_t>(state) % 16 == 0;
-    if (vectors)
-      causal_conv_silu_vec8_kernel<<<dim3(tokens, (C / 8 + 63) / 64), 64, 0, s>>>(a, token_row, tokens);
+    const bool pairs = C % 2 == 0 && x_stride % 2 == 0 && slot_stride % 2 == 0 && w_dtype == DTYPE_F32 &&
+                       reinterpret_cast<uintptr_t>(x) % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 4 == 0 &&
+                       reinterpret_cast<uintptr_t>(state) % 8 == 0;
+    // Tiles pay where requests bring runs of tokens; a step of single tokens has nothing to slide over.
+    if (pairs && tokens >= 4 * rows)
+      causal_conv_silu_tile_kernel<<<dim3((tokens + CONV_TILE - 1) / CONV_TILE, (C / 2 + 63) / 64), 64, 0, s>>>(
+          a, token_row, tokens);
     else
       causal_conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>(a, token_row, tokens);
     if (write_state && taps > 1) conv_state_update_kernel<__nv_bfloat16><<<per_row, 128, 0, s>>>(a);
