@@ -269,6 +269,44 @@ def test_gated_recurrence_and_its_state(cuda_device, heads, dim, vdim):
     assert torch.isnan(state[1]).all()
 
 
+@pytest.mark.parametrize("mode", ["gated", "state_space"])
+def test_long_rows_in_segments_equal_rows_in_one_piece(cuda_device, mode):
+    """Requests of 700, 40 and 300 tokens in segments of 64 that run side by side (a pass from zero, the
+    carry, a pass with outputs) against the same step token by token in one piece: outputs and final
+    states agree to rounding, from states that are not zero."""
+    from zephyr_b200.kernels import ops
+
+    heads, dim, vdim, groups = 4, 48, 40, 2
+    g = torch.Generator().manual_seed(11)
+    lengths = [700, 40, 300]
+    T = sum(lengths)
+    starts, lens = _rows(lengths, cuda_device)
+    slots = torch.tensor([2, 0, 1], dtype=torch.int32, device=cuda_device)
+    dev = lambda t: t.to(cuda_device)
+    start_state = torch.randn(3, heads * dim * vdim, generator=g)
+    status = ops.new_status(cuda_device)
+    if mode == "gated":
+        q, k, v = (dev(torch.randn(T, heads * n, generator=g)) for n in (dim, dim, vdim))
+        z, bias = torch.randn(T, heads * dim, generator=g) + 3.0, dev(torch.randn(heads * dim, generator=g))
+        run = lambda state, segment: ops.decayed_state_scan(
+            "gated", q, k, v, heads, dim, vdim, state, slots, starts, lens, status, decay_logits=dev(z.clone()),
+            decay_bias=bias, inv_tau=0.25, q_scale=0.1, segment=segment)
+    else:
+        q, k = (dev(torch.randn(T, groups * dim, generator=g)) for _ in range(2))
+        v, dt = dev(torch.randn(T, heads * vdim, generator=g)), dev(torch.randn(T, heads, generator=g) - 2.0)
+        consts = [dev(torch.randn(heads, generator=g) * 0.5) for _ in range(3)]
+        run = lambda state, segment: ops.decayed_state_scan(
+            "state_space", q, k, v, heads, dim, vdim, state, slots, starts, lens, status, dt=dt, dt_bias=consts[0],
+            a_log=consts[1], skip=consts[2], heads_per_group=heads // groups, segment=segment)
+    whole_state, cut_state = dev(start_state.clone()), dev(start_state.clone())
+    whole, cut = run(whole_state, 0), run(cut_state, 64)
+    ops.check_status(status)
+    scale = float(whole.abs().max())
+    assert (whole - cut).abs().max().item() < 2e-5 * scale
+    assert (whole_state - cut_state).abs().max().item() < 2e-5 * float(whole_state.abs().max())
+    assert not torch.equal(whole_state.cpu(), start_state)
+
+
 def test_state_space_recurrence_convolution_and_gated_norm(cuda_device):
     """The Mamba-2 path after its input projection, kernel by kernel against the equations: a row cut
     in two (the convolution's last inputs and the state carried in the slot) beside a whole one."""

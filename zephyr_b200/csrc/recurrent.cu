@@ -383,8 +383,39 @@ struct ScanArgs {
   const int* slots; const int* row_q_start; const int* row_q_len;
   int H, D, V, heads_per_group, num_slots, write_state;
   float q_scale;
+  // Long requests in segments that run side by side (seg_len 0: every request is one piece).  Segment g of
+  // a request covers its new tokens g seg_len .. (g + 1) seg_len - 1.  A first pass runs every segment
+  // but a request's last from a zero state and leaves the state it ends with and the product of its
+  // decays per key channel in ws_state / ws_decay; scan_carry_kernel turns those into the true state at
+  // the start of every segment; the second pass runs every segment from there and writes the outputs.
+  int seg_len, segs;                   // segs: segments per request in the grid (an upper bound)
+  float* ws_state;                     // [rows * segs][H][D][V]
+  float* ws_decay;                     // [rows * segs][H][D]
   int* status;
 };
+
+constexpr int SCAN_PASS_OUTPUT = 0;  // from the request's state (or a segment's start state), with outputs
+constexpr int SCAN_PASS_LOCAL = 1;   // from zero, without outputs: what a segment adds, and its decays' product
+
+// ws_state[g] <- the state at the start of segment g + 1: decay(g) * (state at the start of g) + ws_state[g].
+__global__ void scan_carry_kernel(float* ws_state, const float* ws_decay, const float* state, long long slot_stride,
+                                  const int* slots, const int* row_q_len, int segs, int seg_len, int H, int D, int V,
+                                  int num_slots) {
+  const long long per = static_cast<long long>(H) * D * V;
+  const long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int row = blockIdx.y;
+  if (e >= per) return;
+  const int slot = slots[row];
+  if (slot < 0 || slot >= num_slots) return;
+  const int used = (row_q_len[row] + seg_len - 1) / seg_len;
+  const long long channel = e / V;                       // h * D + d
+  float prev = state[static_cast<long long>(slot) * slot_stride + e];
+  for (int g = 0; g + 1 < used; ++g) {
+    const long long at = static_cast<long long>(row) * segs + g;
+    prev = fmaf(ws_decay[at * H * D + channel], prev, ws_state[at * per + e]);
+    ws_state[at * per + e] = prev;
+  }
+}
 
 // z <- sigmoid(z + bias)^(1/tau), through the logarithm: exp(log_sigmoid(z + bias) / tau).
 __global__ void gated_decay_kernel(float* z, long long z_stride, const void* bias, int w_dtype, int width, float inv_tau,
@@ -397,7 +428,7 @@ __global__ void gated_decay_kernel(float* z, long long z_stride, const void* bia
   *at = expf(log_sigmoid_f(*at + load_scale(bias, w_dtype, c)) * inv_tau);
 }
 
-template <typename T, int MODE>
+template <typename T, int MODE, int PASS>
 __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs a) {
   extern __shared__ __align__(16) float scan_smem[];
   const int D = a.D, V = a.V, nwarps = blockDim.x >> 5, Dp = nwarps * SCAN_ROWS;     // blockDim.x == 2 Dp
@@ -407,20 +438,35 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
   float* v_s = q_s + SCAN_CHUNK * Dp;                       // [SCAN_CHUNK][SCAN_COLS]
   float* o_s = v_s + SCAN_CHUNK * SCAN_COLS;                // [SCAN_CHUNK][nwarps][SCAN_COLS]
   float* step_s = o_s + SCAN_CHUNK * nwarps * SCAN_COLS;    // [2][SCAN_CHUNK]: state space: step sizes, decays
-  const int v0 = blockIdx.x * SCAN_COLS, h = blockIdx.y, row = blockIdx.z;
+  const int v0 = blockIdx.x * SCAN_COLS, h = blockIdx.y;
+  const int row = blockIdx.z / a.segs, seg = blockIdx.z - row * a.segs;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slot = a.slots[row];
   if (slot < 0 || slot >= a.num_slots) {
-    if (tid == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
+    if (tid == 0 && seg == 0) report(a.status, STATUS_ROW_OUT_OF_RANGE, slot, row);
     return;
   }
-  const int t0 = a.row_q_start[row], n = a.row_q_len[row];
+  int t0 = a.row_q_start[row], n = a.row_q_len[row];
+  bool last = true;
+  if (a.seg_len > 0) {
+    const int begin = seg * a.seg_len;
+    last = begin + a.seg_len >= n;
+    n = min(n, begin + a.seg_len) - begin;
+    t0 += begin;
+    if (n <= 0 || (PASS == SCAN_PASS_LOCAL && last)) return;      // nothing here, or nobody needs what it adds
+  }
   const int col = v0 + lane, d0 = warp * SCAN_ROWS;
   float* state = a.state + static_cast<long long>(slot) * a.slot_stride + static_cast<long long>(h) * D * V;
-  float S[SCAN_ROWS];
+  const long long piece = static_cast<long long>(row) * a.segs + seg;
+  // Where this piece starts from: zero, the state the carry left for it, or the request's slot.
+  const float* from = PASS == SCAN_PASS_LOCAL ? nullptr
+                      : (a.seg_len > 0 && seg > 0) ? a.ws_state + ((piece - 1) * a.H + h) * D * V : state;
+  float S[SCAN_ROWS], decay_product[PASS == SCAN_PASS_LOCAL ? SCAN_ROWS : 1];
 #pragma unroll
-  for (int d = 0; d < SCAN_ROWS; ++d)
-    S[d] = (d0 + d < D && col < V) ? state[static_cast<long long>(d0 + d) * V + col] : 0.0f;
+  for (int d = 0; d < SCAN_ROWS; ++d) {
+    S[d] = (from != nullptr && d0 + d < D && col < V) ? from[static_cast<long long>(d0 + d) * V + col] : 0.0f;
+    if (PASS == SCAN_PASS_LOCAL) decay_product[d] = 1.0f;
+  }
 
   const T* qp = static_cast<const T*>(a.q);
   const T* kp = static_cast<const T*>(a.k);
@@ -512,16 +558,24 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
         const float4 av = at[d4], kv = kt[d4], qv = qt[d4];
         const int d = 4 * d4;
         S[d] = fmaf(av.x, S[d], kv.x * vt);
-        o0 = fmaf(S[d], qv.x, o0);
         S[d + 1] = fmaf(av.y, S[d + 1], kv.y * vt);
-        o1 = fmaf(S[d + 1], qv.y, o1);
         S[d + 2] = fmaf(av.z, S[d + 2], kv.z * vt);
-        o2 = fmaf(S[d + 2], qv.z, o2);
         S[d + 3] = fmaf(av.w, S[d + 3], kv.w * vt);
-        o3 = fmaf(S[d + 3], qv.w, o3);
+        if (PASS == SCAN_PASS_LOCAL) {
+          decay_product[d] *= av.x;
+          decay_product[d + 1] *= av.y;
+          decay_product[d + 2] *= av.z;
+          decay_product[d + 3] *= av.w;
+        } else {
+          o0 = fmaf(S[d], qv.x, o0);
+          o1 = fmaf(S[d + 1], qv.y, o1);
+          o2 = fmaf(S[d + 2], qv.z, o2);
+          o3 = fmaf(S[d + 3], qv.w, o3);
+        }
       }
-      o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
+      if (PASS != SCAN_PASS_LOCAL) o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
     }
+    if (PASS == SCAN_PASS_LOCAL) continue;
     __syncthreads();
     for (int e = tid; e < nc * SCAN_COLS; e += blockDim.x) {
       const int t = e / SCAN_COLS, l = e - t * SCAN_COLS, c = v0 + l;
@@ -532,7 +586,14 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
       a.out[static_cast<long long>(t0 + c0 + t) * a.H * V + h * V + c] = o;
     }
   }
-  if (a.write_state) {
+  if (PASS == SCAN_PASS_LOCAL) {
+    float* to = a.ws_state + (piece * a.H + h) * D * V;
+#pragma unroll
+    for (int d = 0; d < SCAN_ROWS; ++d) {
+      if (d0 + d < D && col < V) to[static_cast<long long>(d0 + d) * V + col] = S[d];
+      if (d0 + d < D && blockIdx.x == 0 && lane == 0) a.ws_decay[(piece * a.H + h) * D + d0 + d] = decay_product[d];
+    }
+  } else if (a.write_state && last) {
 #pragma unroll
     for (int d = 0; d < SCAN_ROWS; ++d)
       if (d0 + d < D && col < V) state[static_cast<long long>(d0 + d) * V + col] = S[d];
@@ -768,8 +829,11 @@ ZB_API int zb_decayed_state_scan(float* out, const void* q, long long q_stride, 
                                  const void* a_log, const void* skip, int w_dtype, float* state, long long slot_stride,
                                  const int* slots, const int* row_q_start, const int* row_q_len, int rows, int tokens,
                                  int H, int D, int V, int heads_per_group, int num_slots, int write_state,
-                                 float q_scale, float inv_tau, int mode, int dtype, int* status, void* stream) {
-  if (rows < 0 || tokens < 0 || H <= 0 || D <= 0 || V <= 0 || heads_per_group <= 0) return ERR_BAD_ARGUMENT;
+                                 float q_scale, float inv_tau, int mode, int dtype, int seg_len, float* ws_state,
+                                 float* ws_decay, int* status, void* stream) {
+  if (rows < 0 || tokens < 0 || H <= 0 || D <= 0 || V <= 0 || heads_per_group <= 0 || seg_len < 0 ||
+      (seg_len > 0 && (ws_state == nullptr || ws_decay == nullptr)))
+    return ERR_BAD_ARGUMENT;
   if (D > 16 * SCAN_ROWS) return ERR_UNSUPPORTED;
   if (mode != SCAN_GATED && mode != SCAN_STATE_SPACE) return ERR_BAD_ARGUMENT;
   if (rows == 0 || tokens == 0) return OK;
@@ -786,15 +850,26 @@ ZB_API int zb_decayed_state_scan(float* out, const void* q, long long q_stride, 
   a.slots = slots; a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.H = H; a.D = D; a.V = V;
   a.heads_per_group = heads_per_group; a.num_slots = num_slots; a.write_state = write_state; a.q_scale = q_scale;
   a.status = status;
+  a.seg_len = seg_len; a.segs = seg_len > 0 ? (tokens + seg_len - 1) / seg_len : 1;
+  a.ws_state = ws_state; a.ws_decay = ws_decay;
+  if (static_cast<long long>(rows) * a.segs > 65535) return ERR_UNSUPPORTED;
   const int warps = std::max(2, (D + SCAN_ROWS - 1) / SCAN_ROWS);
   const size_t smem = sizeof(float) * (3 * SCAN_CHUNK * warps * SCAN_ROWS + SCAN_CHUNK * SCAN_COLS +
                                        SCAN_CHUNK * warps * SCAN_COLS + 2 * SCAN_CHUNK);
-  const dim3 grid((V + SCAN_COLS - 1) / SCAN_COLS, H, rows);
-#define ZB_SCAN(T, MODE)                                              \
-  {                                                                   \
-    auto kernel = decayed_state_scan_kernel<T, MODE>;                 \
-    if (int rc = allow_shared(kernel, smem)) return rc;               \
-    kernel<<<grid, warps * 32, smem, s>>>(a);                         \
+  const dim3 grid((V + SCAN_COLS - 1) / SCAN_COLS, H, rows * a.segs);
+#define ZB_SCAN(T, MODE)                                                                                       \
+  {                                                                                                            \
+    auto kernel = decayed_state_scan_kernel<T, MODE, SCAN_PASS_OUTPUT>;                                        \
+    if (int rc = allow_shared(kernel, smem)) return rc;                                                        \
+    if (seg_len > 0) {                                                                                         \
+      auto local = decayed_state_scan_kernel<T, MODE, SCAN_PASS_LOCAL>;                                        \
+      if (int rc = allow_shared(local, smem)) return rc;                                                       \
+      local<<<grid, warps * 32, smem, s>>>(a);                                                                 \
+      const long long per = static_cast<long long>(H) * D * V;                                                 \
+      scan_carry_kernel<<<dim3(static_cast<unsigned>((per + 255) / 256), rows), 256, 0, s>>>(                  \
+          ws_state, ws_decay, state, slot_stride, slots, row_q_len, a.segs, seg_len, H, D, V, num_slots);      \
+    }                                                                                                          \
+    kernel<<<grid, warps * 32, smem, s>>>(a);                                                                  \
   }
   if (dtype == DTYPE_F32) {
     if (mode == SCAN_GATED) ZB_SCAN(float, SCAN_GATED) else ZB_SCAN(float, SCAN_STATE_SPACE)

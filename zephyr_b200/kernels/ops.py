@@ -80,7 +80,7 @@ _SIGNATURES = {
     "zb_decayed_state_scan": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_float, c_int, c_int, c_void_p, c_void_p],
+                              c_float, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_gated_group_rms_norm": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                 c_float, c_int, c_int, c_void_p],
     "zb_scaled_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_longlong, c_int, c_int, c_void_p],
@@ -435,6 +435,9 @@ def causal_conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torc
     return out
 
 
+SCAN_SEGMENT = 256     # tokens of a segment when long requests are cut into segments that run side by side
+
+
 def state_scan_max_channels() -> int:
     return library().zb_state_scan_max_channels()
 
@@ -445,14 +448,20 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
                        decay_bias: torch.Tensor | None = None, inv_tau: float = 1.0, q_scale: float = 1.0,
                        dt: torch.Tensor | None = None, dt_bias: torch.Tensor | None = None,
                        a_log: torch.Tensor | None = None, skip: torch.Tensor | None = None, heads_per_group: int = 1,
-                       write_state: bool = True) -> torch.Tensor:
+                       write_state: bool = True, segment: int | None = None) -> torch.Tensor:
     """S_t = diag(a_t) S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per head over each row's new tokens, from and
     to ``state`` [slots, heads * key_dim * value_dim] float32 (rows may be strided); returns o as float32
     [T, heads * value_dim].  q, k, v: [T, .] with unit inner stride, head h at column h * width.
     ``mode`` "gated": a = sigmoid(decay_logits + decay_bias)^inv_tau per key channel (logits float32
     [T, heads * key_dim], overwritten with the decays), q times ``q_scale``.  ``mode`` "state_space": step = softplus(dt + dt_bias),
     a = exp(-exp(a_log) step) per head, k times step, o += skip * v; q and k belong to the head's group
-    (head // heads_per_group at column group * key_dim)."""
+    (head // heads_per_group at column group * key_dim).
+    ``segment``: long requests are cut into segments of this many tokens that run side by side (a pass
+    from zero states, a carry of the state from segment to segment, a pass with the outputs: twice the
+    arithmetic on many times the threads); 0: never; None: chosen, for steps whose requests bring 512
+    tokens and more on average and whose requests x heads x columns / 32 fill less than half the SMs
+    (measured at 8 heads of 128 x 256, one request of 2048 tokens: 539 -> 317 to 345 us; at 16 heads, whose
+    128 CTAs fill the device as they are, 547 -> 617 us)."""
     _cuda(q, k, v, state, slots, row_q_start, row_q_len, status, decay_logits, decay_bias, dt, dt_bias, a_log, skip)
     _i32(slots, row_q_start, row_q_len)
     T = v.shape[0]
@@ -475,13 +484,24 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
             _require(vector is not None, "the state-space mode needs dt_bias, a_log and skip")
             _f32_vector(vector, heads, "a per-head constant")
     out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=v.device)
+    rows = slots.numel()
+    if segment is None:
+        few = 2 * rows * heads * -(-value_dim // 32) <= _sm_count()
+        segment = (max(SCAN_SEGMENT, -(-T // (64 * 16)) * 16)
+                   if few and T >= 4 * SCAN_SEGMENT and T >= 2 * SCAN_SEGMENT * rows else 0)
+    ws_state = ws_decay = None
+    if segment:
+        pieces = rows * -(-T // segment)
+        ws_state = torch.empty((pieces, heads * key_dim * value_dim), dtype=torch.float32, device=v.device)
+        ws_decay = torch.empty((pieces, heads * key_dim), dtype=torch.float32, device=v.device)
     _check(library().zb_decayed_state_scan(
         _ptr(out), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(decay_logits),
         decay_logits.stride(0) if gated else 0, _ptr(decay_bias), _ptr(dt), dt.stride(0) if not gated else 0,
         _ptr(dt_bias), _ptr(a_log), _ptr(skip), 0, _ptr(state), state.stride(0), _ptr(slots), _ptr(row_q_start),
         _ptr(row_q_len), slots.numel(), T, heads, key_dim, value_dim, int(heads_per_group), state.shape[0],
-        int(write_state), float(q_scale), float(inv_tau), 0 if gated else 1, DTYPE_CODE[v.dtype], _ptr(status),
-        _stream()), "decayed_state_scan", kernels=2 if gated else 1)
+        int(write_state), float(q_scale), float(inv_tau), 0 if gated else 1, DTYPE_CODE[v.dtype], int(segment),
+        _ptr(ws_state), _ptr(ws_decay), _ptr(status), _stream()), "decayed_state_scan",
+        kernels=(2 if gated else 1) + (2 if segment else 0))
     return out
 
 

@@ -339,13 +339,14 @@ def state_scan(args) -> dict:
     states = [torch.zeros((R, H * D * V), device=device) for _ in range(_copies(state_bytes) if args.tokens == 0 else 1)]
     bf = torch.bfloat16
     status = ops.new_status(device)
+    segment = None if args.segment < 0 else args.segment
     if args.mode == "gated":
         q, k, v = (torch.randn((T, H * n), device=device, dtype=bf) for n in (D, D, V))
         z, bias = torch.randn((T, H * D), device=device) + 3.0, torch.zeros(H * D, device=device)
 
         def run(i):
             ops.decayed_state_scan("gated", q, k, v, H, D, V, states[i % len(states)], slots, starts, lens, status,
-                                   decay_logits=z, decay_bias=bias, inv_tau=1 / 16, q_scale=D ** -0.5)
+                                   decay_logits=z, decay_bias=bias, inv_tau=1 / 16, q_scale=D ** -0.5, segment=segment)
         read = T * (2 * H * D * 2 + H * V * 2 + H * D * 4)
     else:
         G = max(1, args.kv_heads)
@@ -355,13 +356,14 @@ def state_scan(args) -> dict:
 
         def run(i):
             ops.decayed_state_scan("state_space", q, k, v, H, D, V, states[i % len(states)], slots, starts, lens, status,
-                                   dt=dt, dt_bias=consts[0], a_log=consts[1], skip=consts[2], heads_per_group=H // G)
+                                   dt=dt, dt_bias=consts[0], a_log=consts[1], skip=consts[2], heads_per_group=H // G,
+                                   segment=segment)
         read = T * (2 * G * D * 2 + H * V * 2 + H * 2)
     us = _time(run, args.warmup, args.iters)
     ops.check_status(status, "state_scan")
     moved = 2 * state_bytes + read + T * H * V * 4
     flops = 4 * T * H * D * V          # two multiply-adds per state element and token
-    return {"kernel": "decayed_state_scan_kernel", "mode": args.mode, "rows": R, "tokens": T, "heads": H, "key_dim": D,
+    return {"kernel": "decayed_state_scan_kernel", "mode": args.mode, "segment": args.segment, "rows": R, "tokens": T, "heads": H, "key_dim": D,
             "value_dim": V, "us": round(us, 2), "bytes": moved, "gbs": round(moved / us / 1e3, 1),
             "tflops_fp32": round(flops / us / 1e6, 2)}
 
@@ -448,6 +450,7 @@ def main(argv=None) -> int:
     parser.add_argument("--chunk", type=int, default=0, help="attention: a chunked mask of this size, with sinks")
     parser.add_argument("--value-dim", type=int, default=128, help="state_scan: value channels per head")
     parser.add_argument("--mode", choices=("gated", "state_space"), default="gated")
+    parser.add_argument("--segment", type=int, default=-1, help="state_scan: tokens of a segment (0: one piece; -1: chosen)")
     parser.add_argument("--split", type=int, default=0, help="fixed splits of this many positions in the decode kernel (0: balanced items)")
     parser.add_argument("--rows", type=int, default=8)
     parser.add_argument("--n", type=int, default=6144)
