@@ -354,9 +354,9 @@ __global__ void conv_state_update_kernel(const ConvArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// The recurrence.  A CTA owns one request, one head and 32 value columns; warp w owns the key
-// channels 16 w .. 16 w + 15 of those columns, each lane one column with its 16 state values in
-// registers (two warps per scheduler and more: one warp's shared-memory loads hide behind another's
+// The recurrence.  A CTA owns one request, one head and 64 value columns; warp w owns the key
+// channels 16 w .. 16 w + 15 of those columns, each lane two columns (32 apart) with their 2 x 16 state
+// values in registers, so that a decay, key and query fetched from shared memory serve two columns (two warps per scheduler and more: one warp's shared-memory loads hide behind another's
 // multiply-adds).  The tokens of the request are taken SCAN_CHUNK at a time: decays, keys, queries and
 // values of the chunk lie in shared memory (all float32), every warp runs the chunk's tokens in
 // order, and the warps' partial outputs are added in warp order.  While a chunk runs, the next one's
@@ -364,7 +364,7 @@ __global__ void conv_state_update_kernel(const ConvArgs a) {
 // place of their logits, by a kernel of their own (every CTA of a head would otherwise repeat them).
 constexpr int SCAN_CHUNK = 16;
 constexpr int SCAN_ROWS = 16;        // key channels per warp
-constexpr int SCAN_COLS = 32;        // value columns per CTA
+constexpr int SCAN_COLS = 64;        // value columns per CTA: two a lane, 32 apart
 constexpr int SCAN_V_REGS = SCAN_CHUNK * SCAN_COLS / 64;   // values a thread fetches ahead, at most (a CTA has two warps or more)
 
 constexpr int SCAN_GATED = 0;        // a[d] given per key channel (made from the logits by gated_decay_kernel), q scaled
@@ -455,16 +455,17 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
     t0 += begin;
     if (n <= 0 || (PASS == SCAN_PASS_LOCAL && last)) return;      // nothing here, or nobody needs what it adds
   }
-  const int col = v0 + lane, d0 = warp * SCAN_ROWS;
+  const int col = v0 + lane, col2 = col + 32, d0 = warp * SCAN_ROWS;
   float* state = a.state + static_cast<long long>(slot) * a.slot_stride + static_cast<long long>(h) * D * V;
   const long long piece = static_cast<long long>(row) * a.segs + seg;
   // Where this piece starts from: zero, the state the carry left for it, or the request's slot.
   const float* from = PASS == SCAN_PASS_LOCAL ? nullptr
                       : (a.seg_len > 0 && seg > 0) ? a.ws_state + ((piece - 1) * a.H + h) * D * V : state;
-  float S[SCAN_ROWS], decay_product[PASS == SCAN_PASS_LOCAL ? SCAN_ROWS : 1];
+  float S[SCAN_ROWS], S2[SCAN_ROWS], decay_product[PASS == SCAN_PASS_LOCAL ? SCAN_ROWS : 1];
 #pragma unroll
   for (int d = 0; d < SCAN_ROWS; ++d) {
     S[d] = (from != nullptr && d0 + d < D && col < V) ? from[static_cast<long long>(d0 + d) * V + col] : 0.0f;
+    S2[d] = (from != nullptr && d0 + d < D && col2 < V) ? from[static_cast<long long>(d0 + d) * V + col2] : 0.0f;
     if (PASS == SCAN_PASS_LOCAL) decay_product[d] = 1.0f;
   }
 
@@ -548,11 +549,11 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
     __syncthreads();
     if (c0 + SCAN_CHUNK < n) fetch(c0 + SCAN_CHUNK);      // lands while this chunk runs
     for (int t = 0; t < nc; ++t) {
-      const float vt = v_s[t * SCAN_COLS + lane];
+      const float vt = v_s[t * SCAN_COLS + lane], vt2 = v_s[t * SCAN_COLS + 32 + lane];
       const float4* at = reinterpret_cast<const float4*>(a_s + t * Dp + d0);
       const float4* kt = reinterpret_cast<const float4*>(k_s + t * Dp + d0);
       const float4* qt = reinterpret_cast<const float4*>(q_s + t * Dp + d0);
-      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f, p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
 #pragma unroll
       for (int d4 = 0; d4 < SCAN_ROWS / 4; ++d4) {
         const float4 av = at[d4], kv = kt[d4], qv = qt[d4];
@@ -561,6 +562,10 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
         S[d + 1] = fmaf(av.y, S[d + 1], kv.y * vt);
         S[d + 2] = fmaf(av.z, S[d + 2], kv.z * vt);
         S[d + 3] = fmaf(av.w, S[d + 3], kv.w * vt);
+        S2[d] = fmaf(av.x, S2[d], kv.x * vt2);
+        S2[d + 1] = fmaf(av.y, S2[d + 1], kv.y * vt2);
+        S2[d + 2] = fmaf(av.z, S2[d + 2], kv.z * vt2);
+        S2[d + 3] = fmaf(av.w, S2[d + 3], kv.w * vt2);
         if (PASS == SCAN_PASS_LOCAL) {
           decay_product[d] *= av.x;
           decay_product[d + 1] *= av.y;
@@ -571,9 +576,16 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
           o1 = fmaf(S[d + 1], qv.y, o1);
           o2 = fmaf(S[d + 2], qv.z, o2);
           o3 = fmaf(S[d + 3], qv.w, o3);
+          p0 = fmaf(S2[d], qv.x, p0);
+          p1 = fmaf(S2[d + 1], qv.y, p1);
+          p2 = fmaf(S2[d + 2], qv.z, p2);
+          p3 = fmaf(S2[d + 3], qv.w, p3);
         }
       }
-      if (PASS != SCAN_PASS_LOCAL) o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
+      if (PASS != SCAN_PASS_LOCAL) {
+        o_s[(t * nwarps + warp) * SCAN_COLS + lane] = (o0 + o1) + (o2 + o3);
+        o_s[(t * nwarps + warp) * SCAN_COLS + 32 + lane] = (p0 + p1) + (p2 + p3);
+      }
     }
     if (PASS == SCAN_PASS_LOCAL) continue;
     __syncthreads();
@@ -591,12 +603,15 @@ __global__ void __launch_bounds__(512) decayed_state_scan_kernel(const ScanArgs 
 #pragma unroll
     for (int d = 0; d < SCAN_ROWS; ++d) {
       if (d0 + d < D && col < V) to[static_cast<long long>(d0 + d) * V + col] = S[d];
+      if (d0 + d < D && col2 < V) to[static_cast<long long>(d0 + d) * V + col2] = S2[d];
       if (d0 + d < D && blockIdx.x == 0 && lane == 0) a.ws_decay[(piece * a.H + h) * D + d0 + d] = decay_product[d];
     }
   } else if (a.write_state && last) {
 #pragma unroll
-    for (int d = 0; d < SCAN_ROWS; ++d)
+    for (int d = 0; d < SCAN_ROWS; ++d) {
       if (d0 + d < D && col < V) state[static_cast<long long>(d0 + d) * V + col] = S[d];
+      if (d0 + d < D && col2 < V) state[static_cast<long long>(d0 + d) * V + col2] = S2[d];
+    }
   }
 }
 

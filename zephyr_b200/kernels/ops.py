@@ -435,7 +435,7 @@ def causal_conv_silu(x: torch.Tensor, channels: int, w: torch.Tensor, bias: torc
     return out
 
 
-SCAN_SEGMENT = 256     # tokens of a segment when long requests are cut into segments that run side by side
+SCAN_SEGMENT = 128     # tokens of a segment when long requests are cut into segments that run side by side
 
 
 def state_scan_max_channels() -> int:
@@ -458,10 +458,9 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     (head // heads_per_group at column group * key_dim).
     ``segment``: long requests are cut into segments of this many tokens that run side by side (a pass
     from zero states, a carry of the state from segment to segment, a pass with the outputs: twice the
-    arithmetic on many times the threads); 0: never; None: chosen, for steps whose requests bring 512
-    tokens and more on average and whose requests x heads x columns / 32 fill less than half the SMs
-    (measured at 8 heads of 128 x 256, one request of 2048 tokens: 539 -> 317 to 345 us; at 16 heads, whose
-    128 CTAs fill the device as they are, 547 -> 617 us)."""
+    arithmetic on many times the threads); 0: never; None: chosen, for steps whose requests bring 256
+    tokens and more on average and whose requests x heads x columns / 64 do not fill the SMs (measured,
+    one request of 2048 tokens: 8 heads of 128 x 256: 712 -> 270 us; 16 heads: 720 -> 482 us)."""
     _cuda(q, k, v, state, slots, row_q_start, row_q_len, status, decay_logits, decay_bias, dt, dt_bias, a_log, skip)
     _i32(slots, row_q_start, row_q_len)
     T = v.shape[0]
@@ -486,7 +485,7 @@ def decayed_state_scan(mode: str, q: torch.Tensor, k: torch.Tensor, v: torch.Ten
     out = torch.empty((T, heads * value_dim), dtype=torch.float32, device=v.device)
     rows = slots.numel()
     if segment is None:
-        few = 2 * rows * heads * -(-value_dim // 32) <= _sm_count()
+        few = rows * heads * -(-value_dim // 64) <= _sm_count()
         segment = (max(SCAN_SEGMENT, -(-T // (64 * 16)) * 16)
                    if few and T >= 4 * SCAN_SEGMENT and T >= 2 * SCAN_SEGMENT * rows else 0)
     ws_state = ws_decay = None
