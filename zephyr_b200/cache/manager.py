@@ -29,13 +29,16 @@ NULL_PAGE = 0
 class PagedCacheSpec:
     """A cache that grows with the context: per position and head a key of ``key_dim`` values and a
     value of ``value_dim`` values (the reference keeps the two widths apart per layer,
-    src/include/kv_cache/cache_engine.hpp:18-22).  ``value_dim`` 0 means "as wide as the key"."""
+    src/include/kv_cache/cache_engine.hpp:18-22).  ``value_dim`` 0 means "as wide as the key".
+    ``keys_only``: nothing is stored for the values; the reader takes the keys for them (a latent that is
+    key and value at once), and a page is half as large."""
 
     num_kv_heads: int
     key_dim: int
     value_dim: int = 0
     window: int = 0        # 0: every position is kept; n: only the last n positions are ever read
     chunk: int = 0         # n > 0: a query at position p reads only positions >= (p // n) * n
+    keys_only: bool = False
 
     def __post_init__(self) -> None:
         if self.value_dim == 0:
@@ -51,7 +54,12 @@ class PagedCacheSpec:
 
     @property
     def group_key(self) -> tuple:
-        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window, self.chunk)
+        return ("paged", self.num_kv_heads, self.key_dim, self.value_dim, self.window, self.chunk, self.keys_only)
+
+    @property
+    def stored_per_position(self) -> int:
+        """Elements one position takes in a page, over all heads."""
+        return self.num_kv_heads * (self.key_dim + (0 if self.keys_only else self.value_dim))
 
 
 @dataclass(frozen=True)

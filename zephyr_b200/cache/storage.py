@@ -6,7 +6,8 @@ page_size, head_dim]`` in the model's type: the rows of one page and head lie to
 one contiguous run.  With different widths a page holds its keys ``[kv_heads, page_size, key_dim]``
 and behind them its values ``[kv_heads, page_size, value_dim]``; ``CacheStorage[c]`` is then the
 flat ``[num_pages, elements per page]`` tensor and ``keys(c)`` / ``values(c)`` are views of the two
-halves (for equal widths they are ``[c][:, 0]`` and ``[c][:, 1]``).  The attention kernels of this
+halves (for equal widths they are ``[c][:, 0]`` and ``[c][:, 1]``).  A cache that keeps keys only
+(``PagedCacheSpec.keys_only``) is the flat form with no value half.  The attention kernels of this
 package take equal widths only.  Caches of one group are indexed by the same page ids.  Inside a
 row (the ``head_dim`` values of one position and head) the 16-byte chunks are permuted by the position (``kv_swizzle`` in csrc/common.cuh, mirrored by
 ``kernels.ops.kv_swizzle``): a page copied into shared memory as it is, by one bulk copy, can then be
@@ -25,8 +26,7 @@ from .manager import CacheManager, PagedCacheSpec, StateCacheSpec
 
 
 def paged_cache_bytes_per_page(spec: PagedCacheSpec, page_size: int, dtype: torch.dtype) -> int:
-    return (spec.num_kv_heads * page_size * (spec.key_dim + spec.value_dim)
-            * torch.empty((), dtype=dtype).element_size())
+    return spec.stored_per_position * page_size * torch.empty((), dtype=dtype).element_size()
 
 
 def bytes_per_page(cache_specs, page_size: int, dtype: torch.dtype) -> int:
@@ -43,10 +43,10 @@ class CacheStorage:
             if isinstance(spec, PagedCacheSpec):
                 pages = manager.groups[manager.group_of_cache[cache_id]].pool.num_pages
                 # Zeros, not empty: the null page is read by nothing, but a debugger should see zeros there.
-                if spec.key_dim == spec.value_dim:
+                if spec.key_dim == spec.value_dim and not spec.keys_only:
                     shape = (pages, 2, spec.num_kv_heads, manager.page_size, spec.key_dim)
                 else:
-                    shape = (pages, spec.num_kv_heads * manager.page_size * (spec.key_dim + spec.value_dim))
+                    shape = (pages, manager.page_size * spec.stored_per_position)
                 self.tensors.append(torch.zeros(shape, dtype=dtype, device=device))
             elif isinstance(spec, StateCacheSpec):
                 self.tensors.append(torch.zeros((manager.max_requests, *spec.shape),
@@ -60,6 +60,8 @@ class CacheStorage:
     def keys(self, cache_id: int) -> torch.Tensor:
         """[num_pages, kv_heads, page_size, key_dim]: a view of the pages' key halves."""
         spec, tensor = self.specs[cache_id], self.tensors[cache_id]
+        if spec.keys_only:
+            return tensor.view(tensor.shape[0], spec.num_kv_heads, self.page_size, spec.key_dim)
         if spec.key_dim == spec.value_dim:
             return tensor[:, 0]
         split = spec.num_kv_heads * self.page_size * spec.key_dim
@@ -68,6 +70,8 @@ class CacheStorage:
     def values(self, cache_id: int) -> torch.Tensor:
         """[num_pages, kv_heads, page_size, value_dim]: a view of the pages' value halves."""
         spec, tensor = self.specs[cache_id], self.tensors[cache_id]
+        if spec.keys_only:
+            return self.keys(cache_id)
         if spec.key_dim == spec.value_dim:
             return tensor[:, 1]
         split = spec.num_kv_heads * self.page_size * spec.key_dim

@@ -17,6 +17,9 @@
 // (chunks counted from position 0 of the sequence); `sinks` (one float32 per query head) adds
 // exp(sink) to the softmax's denominator, a term without key or value that is not scaled.
 //
+// `softcap` > 0 bounds the scaled scores smoothly: s <- softcap * tanh(s / softcap).  `shared_kv`: the
+// cache keeps keys only and they serve as the values too (kd = vd; a page is [nkv][page_size][kd]).
+//
 // One CTA serves one tile: a run of consecutive new tokens of one request, one key/value head,
 // and a chunk of that head's query heads.  The (token, head) pairs of the tile are dealt to the
 // warps; key/value tiles of 32 positions are staged in shared memory once and used by all pairs.
@@ -42,6 +45,8 @@ struct AttentionArgs {
   int max_blocks, page_size, num_pages, num_rows;
   int nh, nkv, kd, vd, window, chunk, tile_tokens, heads_per_chunk;
   float scale;
+  float softcap;             // 0: none
+  int shared_kv;             // the keys are the values
   const float* sinks;        // null, or [nh]: exp(sinks[h]) joins the denominator of head h's softmax
   const float* head_slopes;  // null, or [nh]: query head h adds head_slopes[h] * (key position - query position) to its scores
   int* status;
@@ -98,7 +103,8 @@ paged_attention_simt_kernel(const AttentionArgs a) {
   const int kstride = kd + KPad<T>::N;
   float* q_s = reinterpret_cast<float*>(smem_raw);                       // [ATT_MAX_PAIRS][kd]
   T* k_s = reinterpret_cast<T*>(q_s + ATT_MAX_PAIRS * kd);               // [ATT_TILE][kstride]
-  T* v_s = k_s + ATT_TILE * kstride;                                      // [ATT_TILE][vd]
+  T* v_s = a.shared_kv ? k_s : k_s + ATT_TILE * kstride;                  // [ATT_TILE][vd], or the keys again
+  const int vstride = a.shared_kv ? kstride : vd;
 
   const int tile = blockIdx.x, kvh = blockIdx.y, chunk = blockIdx.z;
   const int row = a.tile_row[tile], q0 = a.tile_q0[tile];
@@ -136,7 +142,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
   const int hi = ctx + q0 + n_tok;
   int lo = a.window > 0 ? max(0, ctx + q0 - a.window + 1) : 0;
   if (a.chunk > 0) lo = max(lo, (ctx + q0) / a.chunk * a.chunk);
-  const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (kd + vd);
+  const long long page_elems = static_cast<long long>(a.nkv) * a.page_size * (a.shared_kv ? kd : kd + vd);
   const long long value_part = static_cast<long long>(a.nkv) * a.page_size * kd;
 
   for (int k0 = lo / ATT_TILE * ATT_TILE; k0 < hi; k0 += ATT_TILE) {
@@ -144,7 +150,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
     // Positions outside [lo, hi) hold zeros: a page that was given back, or one that another
     // request used before, is never read.
     stage_rows<T>(k_s, kstride, cache, a, row, kvh, k0, lo, hi, kd, page_elems, 0, tok0);
-    stage_rows<T>(v_s, vd, cache, a, row, kvh, k0, lo, hi, vd, page_elems, value_part, tok0);
+    if (!a.shared_kv) stage_rows<T>(v_s, vd, cache, a, row, kvh, k0, lo, hi, vd, page_elems, value_part, tok0);
     __syncthreads();
 
     const int kp = k0 + lane;
@@ -166,7 +172,9 @@ paged_attention_simt_kernel(const AttentionArgs a) {
         s = fmaf(qp[d], to_float(kr[d]), s);
         s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
       }
-      s = valid ? fmaf(slope, static_cast<float>(kp - qpos), s * a.scale) : -INFINITY;
+      s *= a.scale;
+      if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
+      s = valid ? fmaf(slope, static_cast<float>(kp - qpos), s) : -INFINITY;
       const float new_m = fmaxf(m[i], warp_max(s));      // finite: the tile holds a visible key
       const float pr = valid ? expf(s - new_m) : 0.0f;
       const float corr = expf(m[i] - new_m);             // exp(-inf) = 0 on the first tile
@@ -180,7 +188,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
 #pragma unroll
         for (int c = 0; c < ACC; ++c) {
           const int d = lane + 32 * c;
-          if (d < vd) acc[i][c] = fmaf(pj, to_float(v_s[j * vd + d]), acc[i][c]);
+          if (d < vd) acc[i][c] = fmaf(pj, to_float(v_s[j * vstride + d]), acc[i][c]);
         }
       }
     }
@@ -212,7 +220,7 @@ paged_attention_simt_kernel(const AttentionArgs a) {
 template <typename T, int ACC>
 int attention_simt_launch(const AttentionArgs& a, int n_tiles, int head_chunks, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(ATT_MAX_PAIRS) * a.kd * sizeof(float) +
-                      static_cast<size_t>(ATT_TILE) * (a.kd + a.vd + KPad<T>::N) * sizeof(T);
+                      static_cast<size_t>(ATT_TILE) * (a.kd + (a.shared_kv ? 0 : a.vd) + KPad<T>::N) * sizeof(T);
   auto kernel = paged_attention_simt_kernel<T, ACC>;
   if (smem > 48 * 1024 &&
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
@@ -253,10 +261,11 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
                                    int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
                                    const int* tile_q0, int n_tiles, int tile_tokens, const int* row_q_start,
                                    const int* row_q_len, const int* row_ctx, int nh, int nkv, int kd, int vd,
-                                   int window, int chunk, float scale, const float* head_slopes, const float* sinks,
-                                   int dtype, int* status, void* stream) {
+                                   int window, int chunk, float scale, float softcap, int shared_kv,
+                                   const float* head_slopes, const float* sinks, int dtype, int* status,
+                                   void* stream) {
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || kd <= 0 || vd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0 ||
-      chunk < 0)
+      chunk < 0 || softcap < 0.0f || (shared_kv && kd != vd))
     return ERR_BAD_ARGUMENT;
   if (kd % 2 != 0 || kd > 256 || vd > 256) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
@@ -270,7 +279,7 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   a.row_q_start = row_q_start; a.row_q_len = row_q_len; a.row_ctx = row_ctx;
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
   a.nh = nh; a.nkv = nkv; a.kd = kd; a.vd = vd; a.window = window; a.chunk = chunk; a.tile_tokens = tile_tokens;
-  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.head_slopes = head_slopes; a.sinks = sinks;
+  a.heads_per_chunk = heads_per_chunk; a.scale = scale; a.softcap = softcap; a.shared_kv = shared_kv; a.head_slopes = head_slopes; a.sinks = sinks;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   return dtype == DTYPE_F32 ? attention_simt_dispatch<float>(a, n_tiles, head_chunks, s)

@@ -212,22 +212,29 @@ rmsnorm_warp_rows_kernel(__nv_bfloat16* __restrict__ out, __nv_bfloat16* __restr
   }
 }
 
-// ----------------------------------------------------------------------------- SiLU * up
+// ----------------------------------------------------------------------------- act(gate) * up
+// The gate's activation: 0 = SiLU, z * sigmoid(z); 1 = ReLU.
+constexpr int ACT_SILU = 0;
+constexpr int ACT_RELU = 1;
+__device__ __forceinline__ float gate_act(float g, int act) {
+  return act == ACT_RELU ? fmaxf(g, 0.0f) : g / (1.0f + expf(-g));
+}
+
 // gu is [T, 2I]: columns [0, I) hold the gate, [I, 2I) the up projection.
 template <typename T>
-__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int I) {
+__global__ void silu_mul_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int I, int act) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     const long long t = e / I;
     const int i = static_cast<int>(e - t * I);
     const float g = to_float(gu[t * 2 * I + i]);
     const float u = to_float(gu[t * 2 * I + I + i]);
-    out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    out[e] = from_float<T>(gate_act(g, act) * u);
   }
 }
 
 template <typename T>
-__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total_vec, int I) {
+__global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total_vec, int I, int act) {
   constexpr int N = Vec<T>::N;
   const int per_row = I / N;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -238,7 +245,7 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ g
     load_vec<T>(gu + t * 2 * I + i, g);
     load_vec<T>(gu + t * 2 * I + I + i, u);
 #pragma unroll
-    for (int k = 0; k < N; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+    for (int k = 0; k < N; ++k) g[k] = gate_act(g[k], act) * u[k];
     store_vec<T>(out + t * I + i, g);
   }
 }
@@ -246,7 +253,7 @@ __global__ void silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ g
 // The same for gate and up columns interleaved in blocks of 8: columns [16j, 16j+8) are gate
 // values, [16j+8, 16j+16) the matching up values; out[t, 8j + r] = silu(gate) * up.
 template <typename T>
-__global__ void silu_mul_blocked_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int I) {
+__global__ void silu_mul_blocked_kernel(T* __restrict__ out, const T* __restrict__ gu, long long total, int I, int act) {
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
   for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
     const long long t = e / I;
@@ -254,14 +261,14 @@ __global__ void silu_mul_blocked_kernel(T* __restrict__ out, const T* __restrict
     const long long base = t * 2 * I + (i / 8) * 16 + (i % 8);
     const float g = to_float(gu[base]);
     const float u = to_float(gu[base + 8]);
-    out[e] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    out[e] = from_float<T>(gate_act(g, act) * u);
   }
 }
 
 // One thread per block of 8 outputs: the gate block and the up block are one 16-byte (bfloat16) or
 // two 16-byte (float32) loads each.
 template <typename T>
-__global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, long long blocks8, int I) {
+__global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, long long blocks8, int I, int act) {
   constexpr int N = Vec<T>::N, PARTS = 8 / N;
   const int per_row = I / 8;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -276,7 +283,7 @@ __global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __rest
       load_vec<T>(src + p * N, g);
       load_vec<T>(src + 8 + p * N, u);
 #pragma unroll
-      for (int k = 0; k < N; ++k) g[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+      for (int k = 0; k < N; ++k) g[k] = gate_act(g[k], act) * u[k];
       store_vec<T>(dst + p * N, g);
     }
   }
@@ -285,7 +292,7 @@ __global__ void silu_mul_blocked_vec_kernel(T* __restrict__ out, const T* __rest
 // The same with one block per token row: no division to find the row, and a thread's loads (two
 // blocks of eight outputs where the row has them) are all asked for before the first is used.
 template <typename T>
-__global__ void silu_mul_blocked_rows_kernel(T* __restrict__ out, const T* __restrict__ gu, int I) {
+__global__ void silu_mul_blocked_rows_kernel(T* __restrict__ out, const T* __restrict__ gu, int I, int act) {
   constexpr int N = Vec<T>::N, PARTS = 8 / N;
   const int per_row = I / 8;
   const T* src = gu + static_cast<size_t>(blockIdx.x) * 2 * I;
@@ -309,7 +316,7 @@ __global__ void silu_mul_blocked_rows_kernel(T* __restrict__ out, const T* __res
 #pragma unroll
       for (int p = 0; p < PARTS; ++p) {
 #pragma unroll
-        for (int k = 0; k < N; ++k) g[b][p][k] = g[b][p][k] / (1.0f + expf(-g[b][p][k])) * u[b][p][k];
+        for (int k = 0; k < N; ++k) g[b][p][k] = gate_act(g[b][p][k], act) * u[b][p][k];
         store_vec<T>(dst + (b ? j1 : j0) * 8 + p * N, g[b][p]);
       }
     }
@@ -386,17 +393,17 @@ int rmsnorm_launch(void* out, void* x, const void* delta, const void* w, int w_d
 }
 
 template <typename T>
-int silu_mul_launch(void* out, const void* gu, int T_, int I, cudaStream_t stream) {
+int silu_mul_launch(void* out, const void* gu, int T_, int I, int act, cudaStream_t stream) {
   if (T_ == 0 || I == 0) return OK;
   const int threads = 256;
   if (aligned16<T>(out, I) && aligned16<T>(gu, I)) {
     const long long total = static_cast<long long>(T_) * (I / Vec<T>::N);
     const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
-    silu_mul_vec_kernel<T><<<blocks, threads, 0, stream>>>((T*)out, (const T*)gu, total, I);
+    silu_mul_vec_kernel<T><<<blocks, threads, 0, stream>>>((T*)out, (const T*)gu, total, I, act);
   } else {
     const long long total = static_cast<long long>(T_) * I;
     const int blocks = static_cast<int>(std::min<long long>((total + threads - 1) / threads, 148LL * 16));
-    silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((T*)out, (const T*)gu, total, I);
+    silu_mul_kernel<T><<<blocks, threads, 0, stream>>>((T*)out, (const T*)gu, total, I, act);
   }
   return launch_result();
 }
@@ -449,10 +456,10 @@ ZB_API int zb_add_rmsnorm(void* out, void* residual, const void* delta, const vo
              : rmsnorm_launch<__nv_bfloat16>(out, residual, delta, w, w_dtype, eps, rows, H, H, H, s);
 }
 
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i]; with blocked != 0 gate and up columns alternate in
+// out[t, i] = act(gu[t, i]) * gu[t, I + i], act being SiLU (0) or ReLU (1); with blocked != 0 gate and up columns alternate in
 // blocks of 8 (I a multiple of 8): out[t, 8j + r] = silu(gu[t, 16j + r]) * gu[t, 16j + 8 + r].
-ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int blocked, void* stream) {
-  if (T < 0 || I < 0 || (blocked && I % 8 != 0)) return ERR_BAD_ARGUMENT;
+ZB_API int zb_act_mul(void* out, const void* gu, int T, int I, int dtype, int blocked, int act, void* stream) {
+  if (T < 0 || I < 0 || (blocked && I % 8 != 0) || (act != ACT_SILU && act != ACT_RELU)) return ERR_BAD_ARGUMENT;
   auto s = static_cast<cudaStream_t>(stream);
   if (blocked) {
     if (T == 0 || I == 0) return OK;
@@ -461,23 +468,27 @@ ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int b
       const int per_row = I / 8;
       int threads = ((per_row + 1) / 2 + 31) / 32 * 32;
       threads = threads < 32 ? 32 : (threads > 256 ? 256 : threads);
-      if (dtype == DTYPE_F32) silu_mul_blocked_rows_kernel<float><<<T, threads, 0, s>>>((float*)out, (const float*)gu, I);
-      else silu_mul_blocked_rows_kernel<__nv_bfloat16><<<T, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I);
+      if (dtype == DTYPE_F32) silu_mul_blocked_rows_kernel<float><<<T, threads, 0, s>>>((float*)out, (const float*)gu, I, act);
+      else silu_mul_blocked_rows_kernel<__nv_bfloat16><<<T, threads, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, I, act);
       return launch_result();
     }
     const long long total = vec ? static_cast<long long>(T) * (I / 8) : static_cast<long long>(T) * I;
     const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148LL * 16));
     if (dtype == DTYPE_F32) {
-      if (vec) silu_mul_blocked_vec_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I);
-      else silu_mul_blocked_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I);
+      if (vec) silu_mul_blocked_vec_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I, act);
+      else silu_mul_blocked_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)gu, total, I, act);
     } else {
-      if (vec) silu_mul_blocked_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I);
-      else silu_mul_blocked_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I);
+      if (vec) silu_mul_blocked_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I, act);
+      else silu_mul_blocked_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, total, I, act);
     }
     return launch_result();
   }
-  return dtype == DTYPE_F32 ? silu_mul_launch<float>(out, gu, T, I, s)
-                            : silu_mul_launch<__nv_bfloat16>(out, gu, T, I, s);
+  return dtype == DTYPE_F32 ? silu_mul_launch<float>(out, gu, T, I, act, s)
+                            : silu_mul_launch<__nv_bfloat16>(out, gu, T, I, act, s);
+}
+
+ZB_API int zb_silu_mul(void* out, const void* gu, int T, int I, int dtype, int blocked, void* stream) {
+  return zb_act_mul(out, gu, T, I, dtype, blocked, ACT_SILU, stream);
 }
 
 // y [T, N] (rows ldy apart) += bias [N], the bias bfloat16 or float32.

@@ -1,0 +1,79 @@
+// A product that is block-diagonal over heads:  y[t, h, n] = sum_k x[t, h, k] * W[h, n, k], every head
+// with a matrix of its own ([heads, N, K], rows K apart).  Optionally each head's output is multiplied
+// by the logistic function of one number per token and head (a gate on the head's output).
+//
+// Latent attention uses it twice: the queries of a head are carried into the latent space by the
+// transposed key map of that head (so that scores are taken against the cached latent itself), and the
+// attention's result, a weighted sum of latents per head, is carried out of it by the head's value map.
+//
+// float32 sums in the order of k; W and y in the model's type (y may be float32), x in that type or in
+// float32 (a projection that was left unrounded).
+#include "tile_product.cuh"
+
+namespace zb {
+
+struct HeadLinearArgs {
+  void* y;                // [T, heads * N], rows y_stride apart
+  const void* x;          // [T, heads * K], rows x_stride apart
+  const void* w;          // [heads, N, K]
+  const float* gate;      // null, or one logit per (token, head): gate[t * gate_stride + h]
+  long long x_stride, y_stride, gate_stride;
+  int tokens, heads, N, K;
+};
+
+template <typename X, typename T, typename OUT>
+__global__ void __launch_bounds__(TP_THREADS) head_linear_kernel(const HeadLinearArgs a) {
+  __shared__ TileProductSmem sm;
+  const int t0 = blockIdx.x * TP_BM, n0 = blockIdx.y * TP_BN, head = blockIdx.z;
+  if (threadIdx.x < TP_BM) {
+    const int t = t0 + threadIdx.x;
+    sm.row[threadIdx.x] = t < a.tokens ? static_cast<const X*>(a.x) + t * a.x_stride + static_cast<long long>(head) * a.K
+                                       : nullptr;
+  }
+  const T* w = static_cast<const T*>(a.w) + (static_cast<size_t>(head) * a.N + n0) * a.K;
+  float acc[2][2][4];
+  tile_product<T, false, X>(sm, w, w, a.N - n0, a.K, acc);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    const int t = t0 + 2 * ty + m;
+    if (t >= a.tokens) continue;
+    float mult = 1.0f;
+    if (a.gate != nullptr) mult = 1.0f / (1.0f + expf(-a.gate[t * a.gate_stride + head]));
+    OUT* dst = static_cast<OUT*>(a.y) + t * a.y_stride + static_cast<long long>(head) * a.N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n < a.N) dst[n] = from_float<OUT>(acc[m][0][j] * mult);
+    }
+  }
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+ZB_API int zb_head_linear(void* y, const void* x, const void* w, const float* gate, long long x_stride,
+                          long long y_stride, long long gate_stride, int tokens, int heads, int N, int K, int x_dtype,
+                          int dtype, int out_dtype, void* stream) {
+  if (tokens < 0 || heads <= 0 || N <= 0 || K <= 0 || heads > 65535) return ERR_BAD_ARGUMENT;
+  if (tokens == 0) return OK;
+  HeadLinearArgs a;
+  a.y = y; a.x = x; a.w = w; a.gate = gate; a.x_stride = x_stride; a.y_stride = y_stride; a.gate_stride = gate_stride;
+  a.tokens = tokens; a.heads = heads; a.N = N; a.K = K;
+  const dim3 grid((tokens + TP_BM - 1) / TP_BM, (N + TP_BN - 1) / TP_BN, heads);
+  auto s = static_cast<cudaStream_t>(stream);
+  using bf16 = __nv_bfloat16;
+  if (dtype == DTYPE_F32) {
+    if (out_dtype != DTYPE_F32 || x_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
+    head_linear_kernel<float, float, float><<<grid, TP_THREADS, 0, s>>>(a);
+  } else if (x_dtype == DTYPE_F32) {
+    if (out_dtype == DTYPE_F32) head_linear_kernel<float, bf16, float><<<grid, TP_THREADS, 0, s>>>(a);
+    else head_linear_kernel<float, bf16, bf16><<<grid, TP_THREADS, 0, s>>>(a);
+  } else if (out_dtype == DTYPE_F32) {
+    head_linear_kernel<bf16, bf16, float><<<grid, TP_THREADS, 0, s>>>(a);
+  } else {
+    head_linear_kernel<bf16, bf16, bf16><<<grid, TP_THREADS, 0, s>>>(a);
+  }
+  return launch_result();
+}

@@ -11,6 +11,12 @@
 // may differ in width: a page holds [nkv][page_size][kd] keys and behind them [nkv][page_size][vd]
 // values; rows whose bytes are a multiple of 16 are stored with permuted 16-byte chunks (common.cuh:
 // kv_swizzle), any other width as it is.  One warp per (token, head); a lane owns adjacent pairs.
+//
+// Further forms, each a parameter: a norm without scales (`unit_norm`: x / sqrt(mean(x^2) + eps) on q and
+// k); values that are the keys as projected, before their norm (`values_from_keys`: the projection has
+// no value columns); a multiplier on the normed queries that grows with the position,
+// 1 + coef * ln(floor((p + 1) / every) + 1) (`q_temp_*`); a cache that keeps keys only (vd = 0: its
+// reader takes the keys for values too); and no query heads at all (nh = 0: only the cache is written).
 #include "common.cuh"
 
 namespace zb {
@@ -34,6 +40,10 @@ struct QkvPairsArgs {
   const int* block_table;
   int max_blocks, page_size, num_pages, num_rows;
   int nh, nkv, kd, vd;
+  int unit_norm;             // q and k are normed without scales (q_norm_w and k_norm_w are null)
+  int values_from_keys;      // the value head j is the key head j's columns, un-normed
+  float q_temp_coef;         // 0: no multiplier on the queries
+  int q_temp_every;
   int pairs_aligned;         // every pair of the projection, the bias and the scales may move as one 8-byte value
   int* status;
 };
@@ -58,14 +68,16 @@ template <typename IN, typename T>
 __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairsArgs a) {
   const int t = blockIdx.x, lane = threadIdx.x & 31;
   const int head = blockIdx.y * QP_WARPS + (threadIdx.x >> 5);
-  const int total = a.cache != nullptr ? a.nh + 2 * a.nkv : a.nh;
+  const int total = a.cache != nullptr ? a.nh + (a.vd > 0 ? 2 : 1) * a.nkv : a.nh;
   if (head >= total) return;
   const bool is_q = head < a.nh, is_k = !is_q && head < a.nh + a.nkv;
   const int dim = (is_q || is_k) ? a.kd : a.vd;
   const long long col = is_q ? static_cast<long long>(head) * a.kd
                       : is_k ? static_cast<long long>(a.nh) * a.kd + static_cast<long long>(head - a.nh) * a.kd
-                             : static_cast<long long>(a.nh + a.nkv) * a.kd +
-                                   static_cast<long long>(head - a.nh - a.nkv) * a.vd;
+                      : a.values_from_keys
+                          ? static_cast<long long>(a.nh) * a.kd + static_cast<long long>(head - a.nh - a.nkv) * a.kd
+                          : static_cast<long long>(a.nh + a.nkv) * a.kd +
+                                static_cast<long long>(head - a.nh - a.nkv) * a.vd;
   const IN* src = static_cast<const IN*>(a.qkv) + static_cast<long long>(t) * a.stride + col;
   const int pos = a.positions[t];
 
@@ -90,6 +102,14 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairs
   }
   {
     const float* w = is_q ? a.q_norm_w : (is_k ? a.k_norm_w : nullptr);
+    if (w == nullptr && a.unit_norm && (is_q || is_k)) {
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(dim) + a.eps);
+#pragma unroll
+      for (int k = 0; k < QP_PAIRS; ++k) {
+        x[k][0] *= inv;
+        x[k][1] *= inv;
+      }
+    }
     if (w != nullptr) {
       const float inv = 1.0f / sqrtf(warp_sum(ss) / static_cast<float>(dim) + a.eps);
 #pragma unroll
@@ -117,6 +137,15 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairs
         x[k][0] = u * c - v * s;
         x[k][1] = v * c + u * s;
       }
+    }
+  }
+
+  if (is_q && a.q_temp_coef != 0.0f) {
+    const float m = 1.0f + a.q_temp_coef * logf(static_cast<float>((pos + 1) / a.q_temp_every) + 1.0f);
+#pragma unroll
+    for (int k = 0; k < QP_PAIRS; ++k) {
+      x[k][0] *= m;
+      x[k][1] *= m;
     }
   }
 
@@ -164,10 +193,13 @@ using namespace zb;
 ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const float* bias, const float* q_norm_w,
                         const float* k_norm_w, float eps, const float* freqs, int rot_dims, const int* positions,
                         const int* token_row, void* cache, const int* block_table, int max_blocks, int page_size,
-                        int num_pages, int num_rows, int tokens, int nh, int nkv, int kd, int vd, int in_dtype,
-                        int dtype, int* status, void* stream) {
-  if (tokens < 0 || nh <= 0 || nkv <= 0 || kd <= 0 || vd <= 0 || rot_dims < 0 || rot_dims > kd || rot_dims % 2 != 0 ||
-      page_size <= 0)
+                        int num_pages, int num_rows, int tokens, int nh, int nkv, int kd, int vd, int unit_norm,
+                        int values_from_keys, float q_temp_coef, int q_temp_every, int in_dtype, int dtype,
+                        int* status, void* stream) {
+  if (tokens < 0 || nh < 0 || nkv <= 0 || kd <= 0 || vd < 0 || rot_dims < 0 || rot_dims > kd || rot_dims % 2 != 0 ||
+      page_size <= 0 || (nh == 0 && cache == nullptr) || (values_from_keys && vd != kd) ||
+      (q_temp_coef != 0.0f && q_temp_every <= 0) ||
+      (unit_norm && (q_norm_w != nullptr || k_norm_w != nullptr)))
     return ERR_BAD_ARGUMENT;
   if (kd > 64 * QP_PAIRS || vd > 64 * QP_PAIRS) return ERR_UNSUPPORTED;
   if (tokens == 0) return OK;
@@ -177,10 +209,12 @@ ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const fl
   a.token_row = token_row; a.cache = cache; a.block_table = block_table; a.max_blocks = max_blocks;
   a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows; a.nh = nh; a.nkv = nkv; a.kd = kd;
   a.vd = vd; a.status = status;
+  a.unit_norm = unit_norm; a.values_from_keys = values_from_keys; a.q_temp_coef = q_temp_coef;
+  a.q_temp_every = q_temp_every;
   auto even = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 8 == 0; };
   a.pairs_aligned = kd % 2 == 0 && vd % 2 == 0 && stride % 2 == 0 && even(qkv) && even(bias) && even(q_norm_w) &&
                     even(k_norm_w) && even(q_out) && even(cache);
-  const int heads = cache != nullptr ? nh + 2 * nkv : nh;
+  const int heads = cache != nullptr ? nh + (vd > 0 ? 2 : 1) * nkv : nh;
   const dim3 grid(tokens, (heads + QP_WARPS - 1) / QP_WARPS);
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == DTYPE_F32) {

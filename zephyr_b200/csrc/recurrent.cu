@@ -28,6 +28,11 @@ __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + l
 // ------------------------------------------------------------------------------------------------
 // Layer norm.  One CTA per row; the row sits in shared memory as float32, mean and variance are
 // two passes over it (the variance is the mean of the squared deviations).
+// A norm without a shift passes a null pointer for it.
+__device__ __forceinline__ float load_shift(const void* b, int w_dtype, int i) {
+  return b != nullptr ? load_scale(b, w_dtype, i) : 0.0f;
+}
+
 __device__ __forceinline__ void layer_norm_stats(const float* row, int H, float eps, float* scratch, float& mean,
                                                  float& rstd) {
   float s = 0.0f;
@@ -51,10 +56,11 @@ __global__ void layer_norm_kernel(T* out, const X* x, const void* w, const void*
   float mean, rstd;
   layer_norm_stats(ln_row, H, eps, scratch, mean, rstd);
   for (int i = threadIdx.x; i < H; i += blockDim.x)
-    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w, w_dtype, i), load_scale(b, w_dtype, i)));
+    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w, w_dtype, i), load_shift(b, w_dtype, i)));
 }
 
-// residual += mult * LN(delta; w1, b1); then, if `out`, out = LN(residual; w2, b2).
+// residual += mult * LN(delta; w1, b1); then, if `out`, out = LN(residual; w2, b2), or with a null w2
+// the sum itself in T (what a part that reads the stream unnormed takes).
 template <typename T>
 __global__ void residual_layer_norm_kernel(float* residual, const T* delta, const void* w1, const void* b1, float mult,
                                            T* out, const void* w2, const void* b2, int w_dtype, float eps1, float eps2,
@@ -67,16 +73,17 @@ __global__ void residual_layer_norm_kernel(float* residual, const T* delta, cons
   float mean, rstd;
   layer_norm_stats(ln_row, H, eps1, scratch, mean, rstd);
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float y = fmaf((ln_row[i] - mean) * rstd, load_scale(w1, w_dtype, i), load_scale(b1, w_dtype, i));
+    const float y = fmaf((ln_row[i] - mean) * rstd, load_scale(w1, w_dtype, i), load_shift(b1, w_dtype, i));
     const float r = fmaf(mult, y, residual[base + i]);
     residual[base + i] = r;
     ln_row[i] = r;              // each thread rewrites only the elements it read
+    if (out != nullptr && w2 == nullptr) out[base + i] = from_float<T>(r);     // no second norm: the sum, rounded
   }
-  if (out == nullptr) return;
+  if (out == nullptr || w2 == nullptr) return;
   __syncthreads();
   layer_norm_stats(ln_row, H, eps2, scratch, mean, rstd);
   for (int i = threadIdx.x; i < H; i += blockDim.x)
-    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w2, w_dtype, i), load_scale(b2, w_dtype, i)));
+    out[base + i] = from_float<T>(fmaf((ln_row[i] - mean) * rstd, load_scale(w2, w_dtype, i), load_shift(b2, w_dtype, i)));
 }
 
 // The same two kernels for rows of up to LN_VEC_MAX elements whose length is a multiple of four: a thread
@@ -119,7 +126,7 @@ __device__ __forceinline__ void vec_stats(const float4 (&r)[LN_VEC_ITEMS], int n
 }
 
 __device__ __forceinline__ float4 vec_affine(float4 x, float mean, float rstd, const float* w, const float* b, int at) {
-  const float4 wv = load4(w + at), bv = load4(b + at);
+  const float4 wv = load4(w + at), bv = b != nullptr ? load4(b + at) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
   return make_float4(fmaf((x.x - mean) * rstd, wv.x, bv.x), fmaf((x.y - mean) * rstd, wv.y, bv.y),
                      fmaf((x.z - mean) * rstd, wv.z, bv.z), fmaf((x.w - mean) * rstd, wv.w, bv.w));
 }
@@ -167,9 +174,10 @@ residual_layer_norm_vec_kernel(float* residual, const T* delta, const float* w1,
       const float4 y = vec_affine(r[j], mean, rstd, w1, b1, 4 * i), old = load4(residual + base + 4 * i);
       r[j] = make_float4(fmaf(mult, y.x, old.x), fmaf(mult, y.y, old.y), fmaf(mult, y.z, old.z), fmaf(mult, y.w, old.w));
       store4(residual + base + 4 * i, r[j]);
+      if (out != nullptr && w2 == nullptr) store4(out + base + 4 * i, r[j]);   // no second norm: the sum, rounded
     }
   }
-  if (out == nullptr) return;
+  if (out == nullptr || w2 == nullptr) return;
   vec_stats(r, nv, H, eps2, scratch, mean, rstd);
 #pragma unroll
   for (int j = 0; j < LN_VEC_ITEMS; ++j) {
@@ -186,16 +194,18 @@ inline bool ln_vectors(int H, int w_dtype, std::initializer_list<const void*> po
   return true;
 }
 
+// out = scale * table[id] as float32; `rounded` (may be null) gets the same rows in the table's type.
 template <typename T>
-__global__ void embedding_f32_kernel(float* out, const T* table, const int* ids, int H, int V, int* status) {
+__global__ void embedding_f32_kernel(float* out, T* rounded, const T* table, const int* ids, float scale, int H, int V,
+                                     int* status) {
   const int t = blockIdx.x, id = ids[t];
-  if (id < 0 || id >= V) {
-    if (threadIdx.x == 0) report(status, STATUS_TOKEN_OUT_OF_RANGE, id, t);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[static_cast<size_t>(t) * H + i] = 0.0f;
-    return;
+  const bool ok = id >= 0 && id < V;
+  if (!ok && threadIdx.x == 0) report(status, STATUS_TOKEN_OUT_OF_RANGE, id, t);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = ok ? scale * to_float(table[static_cast<size_t>(id) * H + i]) : 0.0f;
+    out[static_cast<size_t>(t) * H + i] = v;
+    if (rounded != nullptr) rounded[static_cast<size_t>(t) * H + i] = from_float<T>(v);
   }
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    out[static_cast<size_t>(t) * H + i] = to_float(table[static_cast<size_t>(id) * H + i]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -788,15 +798,17 @@ ZB_API int zb_residual_layer_norm(float* residual, const void* delta, const void
   return launch_result();
 }
 
-ZB_API int zb_embedding_f32(float* out, const void* table, const int* ids, int tokens, int H, int V, int dtype,
-                            int* status, void* stream) {
+ZB_API int zb_embedding_f32(float* out, void* rounded, const void* table, const int* ids, float scale, int tokens,
+                            int H, int V, int dtype, int* status, void* stream) {
   if (tokens < 0 || H <= 0 || V <= 0) return ERR_BAD_ARGUMENT;
   if (tokens == 0) return OK;
   auto s = static_cast<cudaStream_t>(stream);
   if (dtype == DTYPE_F32)
-    embedding_f32_kernel<float><<<tokens, 128, 0, s>>>(out, static_cast<const float*>(table), ids, H, V, status);
+    embedding_f32_kernel<float><<<tokens, 128, 0, s>>>(out, static_cast<float*>(rounded), static_cast<const float*>(table),
+                                                       ids, scale, H, V, status);
   else
-    embedding_f32_kernel<__nv_bfloat16><<<tokens, 128, 0, s>>>(out, static_cast<const __nv_bfloat16*>(table), ids, H, V,
+    embedding_f32_kernel<__nv_bfloat16><<<tokens, 128, 0, s>>>(out, static_cast<__nv_bfloat16*>(rounded),
+                                                               static_cast<const __nv_bfloat16*>(table), ids, scale, H, V,
                                                                status);
   return launch_result();
 }

@@ -1,0 +1,301 @@
+// A routed feed-forward (mixture of experts), token choice:
+//
+//   s = softmax(z) over all router outputs          (float32; z = router logits)
+//   choice = s + correction                         (moves the choice only)
+//   the `top` outputs with the largest choice are taken (ties: the lower index), each with weight s
+//   (not renormalised);
+//   out = sum over the taken outputs of  s_e * expert_e(x),
+//
+// where the first `experts` outputs are gated feed-forwards down_e(act(gate_e x) * (up_e x)) and the
+// remaining ones are identity experts, expert(x) = x, which have no weights.
+//
+// Four steps, all shapes fixed by the step's token count (nothing is read back by the host):
+//   route     one warp per token: softmax, choice, selection -> ids [T, top], weights [T, top]
+//   align     one CTA: the (token, choice) slots sorted by expert, every expert's run cut into tiles of
+//             TP_BM rows -> slot list, tile list
+//   products  one CTA per (tile, 64 outputs): gate and up together with the activation, then down,
+//             each row's sums in the order of k, so a token's result does not depend on what else
+//             was routed to its expert
+//   combine   out[t] = sum_j weight[t, j] * (expert output of slot (t, j), or x[t] for an identity
+//             expert), in float32 and in the order of j, rounded once.
+#include "tile_product.cuh"
+
+namespace zb {
+
+constexpr int ROUTE_PER_LANE = 8;      // up to 256 router outputs
+constexpr int ROUTE_WARPS = 4;
+
+// ---------------------------------------------------------------------------------------------- route
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
+             int tokens, int outputs, int top) {
+  const int t = blockIdx.x * ROUTE_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  const float* z = logits + t * logits_stride;
+  float s[ROUTE_PER_LANE], c[ROUTE_PER_LANE];
+  float top_z = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < outputs ? z[e] : -INFINITY;
+    top_z = fmaxf(top_z, s[i]);
+  }
+  top_z = warp_max(top_z);
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = e < outputs ? expf(s[i] - top_z) : 0.0f;
+    sum += s[i];
+  }
+  sum = warp_sum(sum);
+#pragma unroll
+  for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+    const int e = lane + 32 * i;
+    s[i] = s[i] / sum;
+    c[i] = e < outputs ? s[i] + (correction != nullptr ? correction[e] : 0.0f) : -INFINITY;
+  }
+  for (int j = 0; j < top; ++j) {
+    // The largest remaining choice; among equals the lowest index.
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (c[i] > best || (c[i] == best && e < best_e && c[i] > -INFINITY)) {
+        best = c[i];
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) {
+        best = other;
+        best_e = other_e;
+      }
+    }
+    float w = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ROUTE_PER_LANE; ++i)
+      if (lane + 32 * i == best_e) {
+        w = s[i];
+        c[i] = -INFINITY;
+      }
+    w = __shfl_sync(0xffffffffu, w, best_e & 31);
+    if (lane == 0) {
+      ids[static_cast<size_t>(t) * top + j] = best_e;
+      weights[static_cast<size_t>(t) * top + j] = w;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------- align
+// plan: [0] = number of tiles; then per tile (expert, first place in `slots`, rows).  slots: the slot
+// numbers (t * top + j) of all choices of real experts, expert after expert.  place_of_slot[slot] says
+// where the slot landed (-1 for an identity expert).
+constexpr int ALIGN_THREADS = 1024;
+
+__global__ void __launch_bounds__(ALIGN_THREADS)
+align_kernel(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts, int max_tiles) {
+  extern __shared__ int align_smem[];
+  int* count = align_smem;                 // [experts]
+  int* start = count + experts;            // [experts + 1]
+  int* fill = start + experts + 1;         // [experts]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = fill[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < num_slots; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = at;
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += TP_BM, ++tiles) {
+        plan[1 + 3 * tiles] = e;
+        plan[2 + 3 * tiles] = at + r;
+        plan[3 + 3 * tiles] = min(TP_BM, count[e] - r);
+      }
+      at += count[e];
+    }
+    start[experts] = at;
+    plan[0] = tiles;
+  }
+  __syncthreads();
+  // Which place a slot gets inside its expert's run depends on the order of arrival; no result does:
+  // every row of a product is summed on its own.
+  for (int i = threadIdx.x; i < num_slots; i += blockDim.x) {
+    const int e = ids[i];
+    int place = -1;
+    if (e >= 0 && e < experts) {
+      place = start[e] + atomicAdd(&fill[e], 1);
+      slots[place] = i;
+    }
+    place_of_slot[i] = place;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- products
+struct ExpertProductArgs {
+  void* out;               // gate/up: hidden [places, ff] in T; down: y [places, width] in float32
+  const void* x;           // gate/up: the tokens [T, width]; down: hidden [places, ff]
+  const void* w0;          // [experts, N, K]
+  const void* w1;          // the up matrices (gate/up only)
+  const int* plan;
+  const int* slots;
+  long long x_stride;
+  int N, K, top, act;
+};
+
+__device__ __forceinline__ float expert_act(float g, int act) {
+  return act == 1 ? fmaxf(g, 0.0f) : g / (1.0f + expf(-g));
+}
+
+// hidden[place, n] = act(gate_e x_t) * (up_e x_t) for the tile's places; x_t is gathered by slot / top.
+template <typename T>
+__global__ void __launch_bounds__(TP_THREADS) expert_gate_up_kernel(const ExpertProductArgs a) {
+  __shared__ TileProductSmem sm;
+  const int tile = blockIdx.x;
+  if (tile >= a.plan[0]) return;
+  const int expert = a.plan[1 + 3 * tile], place0 = a.plan[2 + 3 * tile], rows = a.plan[3 + 3 * tile];
+  const int n0 = blockIdx.y * TP_BN;
+  if (threadIdx.x < TP_BM) {
+    const T* src = nullptr;
+    if (static_cast<int>(threadIdx.x) < rows)
+      src = static_cast<const T*>(a.x) + static_cast<long long>(a.slots[place0 + threadIdx.x] / a.top) * a.x_stride;
+    sm.row[threadIdx.x] = src;
+  }
+  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  float acc[2][2][4];
+  tile_product<T, true>(sm, static_cast<const T*>(a.w0) + w_at, static_cast<const T*>(a.w1) + w_at, a.N - n0, a.K, acc);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    const int r = 2 * ty + m;
+    if (r >= rows) continue;
+    T* dst = static_cast<T*>(a.out) + static_cast<size_t>(place0 + r) * a.N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      // The gate is rounded to the model's type before its activation, as a separate product would leave it.
+      if (n < a.N) dst[n] = from_float<T>(expert_act(to_float(from_float<T>(acc[m][0][j])), a.act) *
+                                          to_float(from_float<T>(acc[m][1][j])));
+    }
+  }
+}
+
+// y[place, n] = down_e hidden[place]  (float32).
+template <typename T>
+__global__ void __launch_bounds__(TP_THREADS) expert_down_kernel(const ExpertProductArgs a) {
+  __shared__ TileProductSmem sm;
+  const int tile = blockIdx.x;
+  if (tile >= a.plan[0]) return;
+  const int expert = a.plan[1 + 3 * tile], place0 = a.plan[2 + 3 * tile], rows = a.plan[3 + 3 * tile];
+  const int n0 = blockIdx.y * TP_BN;
+  if (threadIdx.x < TP_BM)
+    sm.row[threadIdx.x] = static_cast<int>(threadIdx.x) < rows
+                              ? static_cast<const T*>(a.x) + static_cast<long long>(place0 + threadIdx.x) * a.x_stride
+                              : nullptr;
+  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  float acc[2][2][4];
+  tile_product<T, false>(sm, static_cast<const T*>(a.w0) + w_at, nullptr, a.N - n0, a.K, acc);
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+#pragma unroll
+  for (int m = 0; m < 2; ++m) {
+    const int r = 2 * ty + m;
+    if (r >= rows) continue;
+    float* dst = static_cast<float*>(a.out) + static_cast<size_t>(place0 + r) * a.N;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n < a.N) dst[n] = acc[m][0][j];
+    }
+  }
+}
+
+// -------------------------------------------------------------------------------------------- combine
+template <typename T>
+__global__ void combine_kernel(T* out, const float* y, const T* x, long long x_stride, const int* ids,
+                               const float* weights, const int* place_of_slot, int width, int top) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float sum = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      const int slot = t * top + j, place = place_of_slot[slot];
+      const float w = weights[slot];
+      // An expert's output takes the model's type before it is weighted, as a layer of its own would leave it.
+      const float v = place >= 0 ? to_float(from_float<T>(y[static_cast<size_t>(place) * width + i]))
+                                 : to_float(x[t * x_stride + i]);
+      sum = fmaf(w, v, sum);
+    }
+    out[static_cast<size_t>(t) * width + i] = from_float<T>(sum);
+  }
+}
+
+}  // namespace zb
+
+using namespace zb;
+
+ZB_API int zb_route_max_outputs() { return 32 * ROUTE_PER_LANE; }
+ZB_API int zb_expert_tile_rows() { return TP_BM; }
+
+ZB_API int zb_route(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
+                    int tokens, int outputs, int top, void* stream) {
+  if (tokens < 0 || outputs <= 0 || top <= 0 || top > outputs) return ERR_BAD_ARGUMENT;
+  if (outputs > 32 * ROUTE_PER_LANE) return ERR_UNSUPPORTED;
+  if (tokens == 0) return OK;
+  route_kernel<<<(tokens + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, weights, logits, logits_stride, correction, tokens, outputs, top);
+  return launch_result();
+}
+
+ZB_API int zb_route_align(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts,
+                          int max_tiles, void* stream) {
+  if (num_slots < 0 || experts <= 0 || max_tiles < 0) return ERR_BAD_ARGUMENT;
+  const size_t smem = (3 * static_cast<size_t>(experts) + 1) * sizeof(int);
+  if (smem > 48 * 1024) return ERR_UNSUPPORTED;
+  align_kernel<<<1, ALIGN_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(plan, slots, place_of_slot, ids,
+                                                                                num_slots, experts, max_tiles);
+  return launch_result();
+}
+
+// `down` = 0: hidden = act(gate x) * (up x), N = ff, K = width; 1: y = down hidden, N = width, K = ff.
+ZB_API int zb_expert_product(void* out, const void* x, long long x_stride, const void* w0, const void* w1,
+                             const int* plan, const int* slots, int max_tiles, int N, int K, int top, int act,
+                             int down, int dtype, void* stream) {
+  if (max_tiles < 0 || N <= 0 || K <= 0 || top <= 0 || (act != 0 && act != 1)) return ERR_BAD_ARGUMENT;
+  if (max_tiles == 0) return OK;
+  ExpertProductArgs a;
+  a.out = out; a.x = x; a.w0 = w0; a.w1 = w1; a.plan = plan; a.slots = slots; a.x_stride = x_stride;
+  a.N = N; a.K = K; a.top = top; a.act = act;
+  const dim3 grid(max_tiles, (N + TP_BN - 1) / TP_BN);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (down) {
+    if (dtype == DTYPE_F32) expert_down_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
+    else expert_down_kernel<__nv_bfloat16><<<grid, TP_THREADS, 0, s>>>(a);
+  } else {
+    if (dtype == DTYPE_F32) expert_gate_up_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
+    else expert_gate_up_kernel<__nv_bfloat16><<<grid, TP_THREADS, 0, s>>>(a);
+  }
+  return launch_result();
+}
+
+ZB_API int zb_route_combine(void* out, const float* y, const void* x, long long x_stride, const int* ids,
+                            const float* weights, const int* place_of_slot, int tokens, int width, int top, int dtype,
+                            void* stream) {
+  if (tokens < 0 || width <= 0 || top <= 0) return ERR_BAD_ARGUMENT;
+  if (tokens == 0) return OK;
+  auto s = static_cast<cudaStream_t>(stream);
+  const int threads = width >= 1024 ? 256 : 128;
+  if (dtype == DTYPE_F32)
+    combine_kernel<float><<<tokens, threads, 0, s>>>(static_cast<float*>(out), y, static_cast<const float*>(x), x_stride,
+                                                     ids, weights, place_of_slot, width, top);
+  else
+    combine_kernel<__nv_bfloat16><<<tokens, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), y,
+                                                             static_cast<const __nv_bfloat16*>(x), x_stride, ids, weights,
+                                                             place_of_slot, width, top);
+  return launch_result();
+}

@@ -54,6 +54,17 @@ _SIGNATURES = {
                    c_void_p],
     "zb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_void_p],
     "zb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_act_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_head_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int,
+                       c_int, c_int, c_int, c_int, c_void_p],
+    "zb_route_max_outputs": [],
+    "zb_expert_tile_rows": [],
+    "zb_route": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_route_align": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_expert_product": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_void_p],
+    "zb_route_combine": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_int, c_void_p],
     "zb_add_bias": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -65,14 +76,14 @@ _SIGNATURES = {
     "zb_attention_simt_tile_tokens": [c_int],
     "zb_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     "zb_qkv_pairs": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
-                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                     c_int, c_void_p, c_void_p],
+                     c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
     "zb_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p],
     "zb_residual_layer_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int,
                                c_float, c_float, c_int, c_int, c_int, c_void_p],
-    "zb_embedding_f32": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "zb_embedding_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "zb_causal_conv_silu": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                             c_void_p],
@@ -338,9 +349,15 @@ def add_bias(y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     return y
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bool = False) -> torch.Tensor:
-    """silu(gate_up[:, :I]) * gate_up[:, I:] for a contiguous [T, 2I] tensor.  With ``blocked`` the gate
-    and up columns alternate in blocks of 8 (the layout ``gemm_small(..., swiglu=True)`` reads)."""
+ACTIVATIONS = {"silu": 0, "relu": 1}
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bool = False,
+             act: str = "silu") -> torch.Tensor:
+    """act(gate_up[:, :I]) * gate_up[:, I:] for a contiguous [T, 2I] tensor, ``act`` being "silu" or "relu".
+    With ``blocked`` the gate and up columns alternate in blocks of 8 (the layout
+    ``gemm_small(..., swiglu=True)`` reads)."""
+    _require(act in ACTIVATIONS, f"the gate's activation is one of {sorted(ACTIVATIONS)}")
     _cuda(gate_up)
     _require(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.dtype in DTYPE_CODE
              and gate_up.shape[1] % 2 == 0, "gate_up must be a contiguous [T, 2I] tensor")
@@ -349,8 +366,8 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, blocked: bo
         out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
     _require(out.shape == (T, two_i // 2) and out.dtype == gate_up.dtype and out.is_contiguous(), "out must be [T, I]")
     _require(not blocked or (two_i // 2) % 8 == 0, "the blocked layout needs I to be a multiple of 8")
-    _check(library().zb_silu_mul(_ptr(out), _ptr(gate_up), T, two_i // 2, DTYPE_CODE[gate_up.dtype], int(blocked),
-                                 _stream()), "silu_mul")
+    _check(library().zb_act_mul(_ptr(out), _ptr(gate_up), T, two_i // 2, DTYPE_CODE[gate_up.dtype], int(blocked),
+                                ACTIVATIONS[act], _stream()), "silu_mul")
     return out
 
 
@@ -360,10 +377,10 @@ def _f32_vector(v: torch.Tensor | None, size: int, what: str) -> None:
              f"{what} must be a contiguous float32 tensor of {size} values")
 
 
-def layer_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
+def layer_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None, eps: float,
                out_dtype: torch.dtype | None = None) -> torch.Tensor:
     """(x - mean) / sqrt(var + eps) * w + b over the last dimension of a contiguous [rows, H]; x float32 or
-    bfloat16, the result in ``out_dtype`` (default: x's type); w and b float32."""
+    bfloat16, the result in ``out_dtype`` (default: x's type); w and b float32; ``b`` None: no shift."""
     _cuda(x, w, b)
     _require(x.dim() == 2 and x.is_contiguous() and x.dtype in DTYPE_CODE, "x must be a contiguous [rows, H]")
     rows, H = x.shape
@@ -375,11 +392,13 @@ def layer_norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, eps: float,
     return out
 
 
-def residual_layer_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor, eps1: float,
-                        mult: float, w2: torch.Tensor | None = None, b2: torch.Tensor | None = None,
-                        eps2: float = 0.0) -> torch.Tensor | None:
-    """residual (float32, in place) += mult * LN(delta; w1, b1); with w2 and b2 also returns
-    LN(residual; w2, b2) in delta's type: the sum and the next norm in one pass over the row."""
+def residual_layer_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.Tensor, b1: torch.Tensor | None,
+                        eps1: float, mult: float, w2: torch.Tensor | None = None, b2: torch.Tensor | None = None,
+                        eps2: float = 0.0, rounded_sum: bool = False) -> torch.Tensor | None:
+    """residual (float32, in place) += mult * LN(delta; w1, b1); with w2 (and b2, if that norm has a shift)
+    also returns LN(residual; w2, b2) in delta's type: the sum and the next norm in one pass over the row.
+    With ``rounded_sum`` and no w2 it returns the sum itself in delta's type, for a part that reads the
+    stream as it is.  ``b1`` None: the first norm has no shift."""
     _cuda(residual, delta, w1, b1, w2, b2)
     _require(residual.dim() == 2 and residual.is_contiguous() and residual.dtype == torch.float32
              and delta.shape == residual.shape and delta.is_contiguous() and delta.dtype in DTYPE_CODE,
@@ -387,24 +406,27 @@ def residual_layer_norm(residual: torch.Tensor, delta: torch.Tensor, w1: torch.T
     rows, H = residual.shape
     for vector in (w1, b1, w2, b2):
         _f32_vector(vector, H, "scales and shifts")
-    _require((w2 is None) == (b2 is None), "the second norm needs scale and shift")
-    out = torch.empty_like(delta) if w2 is not None else None
+    _require(b2 is None or w2 is not None, "a shift comes with a scale")
+    out = torch.empty_like(delta) if (w2 is not None or rounded_sum) else None
     _check(library().zb_residual_layer_norm(_ptr(residual), _ptr(delta), _ptr(w1), _ptr(b1), float(mult), _ptr(out),
                                             _ptr(w2), _ptr(b2), 0, float(eps1), float(eps2), rows, H,
                                             DTYPE_CODE[delta.dtype], _stream()), "residual_layer_norm")
     return out
 
 
-def embedding_f32(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor) -> torch.Tensor:
-    """Rows of the table as float32 [T, H]: the start of a float32 residual stream."""
+def embedding_f32(table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor, scale: float = 1.0,
+                  rounded: bool = False):
+    """``scale`` times the rows of the table as float32 [T, H]: the start of a float32 residual stream.
+    With ``rounded`` returns (float32 rows, the same rows in the table's type)."""
     _cuda(table, ids, status)
     _i32(ids)
     _require(table.dim() == 2 and table.is_contiguous() and table.dtype in DTYPE_CODE, "table must be [V, H]")
     V, H = table.shape
     out = torch.empty((ids.numel(), H), dtype=torch.float32, device=table.device)
-    _check(library().zb_embedding_f32(_ptr(out), _ptr(table), _ptr(ids), ids.numel(), H, V, DTYPE_CODE[table.dtype],
-                                      _ptr(status), _stream()), "embedding_f32")
-    return out
+    copy = torch.empty((ids.numel(), H), dtype=table.dtype, device=table.device) if rounded else None
+    _check(library().zb_embedding_f32(_ptr(out), _ptr(copy), _ptr(table), _ptr(ids), float(scale), ids.numel(), H, V,
+                                      DTYPE_CODE[table.dtype], _ptr(status), _stream()), "embedding_f32")
+    return (out, copy) if rounded else out
 
 
 CONV_MAX_TAPS = 8
@@ -640,7 +662,7 @@ def attention_tile_tokens(group: int) -> int:
 
 def _cache_geometry(kv_cache: torch.Tensor, nkv: int, kd: int, vd: int, dtype: torch.dtype) -> tuple[int, int]:
     """(pages, page size) of a cache whose pages hold [nkv][page][kd] keys and then [nkv][page][vd] values:
-    the five-dimensional form for equal widths, or flat pages."""
+    the five-dimensional form for equal widths, or flat pages (``vd`` 0: pages of keys alone)."""
     _require(kv_cache.is_contiguous() and kv_cache.dtype == dtype, "a cache must be contiguous and of the model's type")
     if kv_cache.dim() == 5:
         _require(kd == vd, "a [pages, 2, kv_heads, page_size, head_dim] cache has one width")
@@ -657,13 +679,15 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
                     row_ctx: torch.Tensor, nh: int, nkv: int, hd: int, window: int, scale: float,
                     status: torch.Tensor, out: torch.Tensor | None = None,
                     head_slopes: torch.Tensor | None = None, value_dim: int | None = None, chunk: int = 0,
-                    sinks: torch.Tensor | None = None) -> torch.Tensor:
+                    sinks: torch.Tensor | None = None, softcap: float = 0.0, shared_kv: bool = False) -> torch.Tensor:
     """The general kernel: causal attention of every new token over its request's pages.
     ``head_slopes`` (float32 [nh]): query head h adds head_slopes[h] * (key position - query position)
     to its scores, a position encoding that is a bias on the scores.  ``value_dim``: the width of the
     values where it differs from the keys' ``hd``.  ``chunk`` > 0: a query sees only the keys of its own
     run of ``chunk`` positions, runs counted from position 0.  ``sinks`` (float32 [nh]): exp(sinks[h])
-    joins the denominator of head h's softmax."""
+    joins the denominator of head h's softmax.  ``softcap`` > 0: scaled scores become
+    softcap * tanh(score / softcap).  ``shared_kv``: the cache keeps keys only (flat pages
+    [kv_heads * page_size * hd]) and they are the values too."""
     _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, head_slopes, sinks)
     for per_head in (head_slopes, sinks):
         _require(per_head is None or (per_head.dtype == torch.float32 and per_head.is_contiguous()
@@ -671,30 +695,38 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     vd = hd if value_dim is None else int(value_dim)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype in DTYPE_CODE, "q shape")
-    pages, page_size = _cache_geometry(kv_cache, nkv, hd, vd, q.dtype)
+    _require(not shared_kv or vd == hd, "keys that serve as values have the values' width")
+    pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0 if shared_kv else vd, q.dtype)
     if out is None:
         out = torch.empty((q.shape[0], nh * vd), dtype=q.dtype, device=q.device)
     _require(out.shape == (q.shape[0], nh * vd) and out.dtype == q.dtype and out.is_contiguous(), "out must be [T, heads * value_dim]")
     _check(library().zb_paged_attention_simt(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
         block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), int(tile_tokens), _ptr(row_q_start),
-        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, vd, int(window), int(chunk), float(scale), _ptr(head_slopes),
-        _ptr(sinks), DTYPE_CODE[q.dtype], _ptr(status), _stream()), "paged_attention")
+        _ptr(row_q_len), _ptr(row_ctx), nh, nkv, hd, vd, int(window), int(chunk), float(scale), float(softcap),
+        int(shared_kv), _ptr(head_slopes), _ptr(sinks), DTYPE_CODE[q.dtype], _ptr(status), _stream()), "paged_attention")
     return out
 
 
 def qkv_pairs(qkv: torch.Tensor, nh: int, nkv: int, kd: int, vd: int, bias: torch.Tensor | None,
               q_norm_w: torch.Tensor | None, k_norm_w: torch.Tensor | None, eps: float, freqs: torch.Tensor | None,
               rot_dims: int, positions: torch.Tensor, token_row: torch.Tensor, kv_cache: torch.Tensor | None,
-              block_table: torch.Tensor, status: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+              block_table: torch.Tensor, status: torch.Tensor, dtype: torch.dtype, unit_norm: bool = False,
+              values_from_keys: bool = False, q_temp: tuple[float, int] | None = None) -> torch.Tensor | None:
     """Bias, per-head RMS norm of q and k, rotation of adjacent pairs by position * freqs on the first
     ``rot_dims`` dimensions, and the cache write of k and v (keys ``kd`` wide, values ``vd``); returns the
     queries [T, nh * kd] in ``dtype``.  ``qkv`` may be float32 whatever ``dtype`` is; bias, norm scales and
-    frequencies are float32.  Without ``kv_cache`` only the queries are made."""
+    frequencies are float32.  Without ``kv_cache`` only the queries are made.
+
+    ``unit_norm``: q and k are divided by their root mean square and no scale follows.
+    ``values_from_keys``: ``qkv`` has no value columns; the values are the keys as projected (before
+    their norm).  ``q_temp`` = (coef, every): the normed queries are multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1) at position p.  ``vd`` 0: the cache keeps keys only.
+    ``nh`` 0: there are no queries, only the cache is written (returns None)."""
     _cuda(qkv, bias, q_norm_w, k_norm_w, freqs, positions, token_row, kv_cache, block_table, status)
     _i32(positions, token_row, block_table)
     T = qkv.shape[0]
-    width = nh * kd + (nkv * (kd + vd) if kv_cache is not None else 0)
+    width = nh * kd + (nkv * (kd + (0 if values_from_keys else vd)) if kv_cache is not None else 0)
     _require(qkv.dim() == 2 and qkv.shape[1] >= width and qkv.stride(1) == 1 and qkv.dtype in DTYPE_CODE,
              "qkv must be [T, heads*key_dim + kv_heads*(key_dim + value_dim)] with unit inner stride")
     for vector, size in ((bias, width), (q_norm_w, kd), (k_norm_w, kd), (freqs, rot_dims // 2)):
@@ -704,12 +736,13 @@ def qkv_pairs(qkv: torch.Tensor, nh: int, nkv: int, kd: int, vd: int, bias: torc
     pages, page_size = (0, 1)
     if kv_cache is not None:
         pages, page_size = _cache_geometry(kv_cache, nkv, kd, vd, dtype)
-    q_out = torch.empty((T, nh * kd), dtype=dtype, device=qkv.device)
+    q_out = torch.empty((T, nh * kd), dtype=dtype, device=qkv.device) if nh > 0 else None
+    coef, every = (float(q_temp[0]), int(q_temp[1])) if q_temp is not None else (0.0, 1)
     _check(library().zb_qkv_pairs(
         _ptr(q_out), _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(freqs),
         int(rot_dims), _ptr(positions), _ptr(token_row), _ptr(kv_cache), _ptr(block_table), block_table.shape[1],
-        page_size, pages, block_table.shape[0], T, nh, nkv, kd, vd, DTYPE_CODE[qkv.dtype], DTYPE_CODE[dtype],
-        _ptr(status), _stream()), "qkv_pairs")
+        page_size, pages, block_table.shape[0], T, nh, nkv, kd, vd, int(unit_norm), int(values_from_keys), coef,
+        every, DTYPE_CODE[qkv.dtype], DTYPE_CODE[dtype], _ptr(status), _stream()), "qkv_pairs")
     return q_out
 
 
@@ -1189,6 +1222,85 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     if out_dtype is None or out_dtype == x.dtype:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------------------- products per head and per expert
+def head_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+                gate: torch.Tensor | None = None) -> torch.Tensor:
+    """y[t, h, :] = w[h] x[t, h, :] for x [T, heads * K] (unit inner stride) and w [heads, N, K]: a product
+    that is block-diagonal over heads; returns [T, heads * N] in ``out_dtype`` (default: w's type).  x may be
+    float32 beside bfloat16 matrices.  ``gate`` (float32 [T, >= heads], unit inner stride): head h's output
+    is multiplied by sigmoid(gate[t, h]).  float32 sums in the order of k."""
+    _cuda(x, w, gate)
+    heads, N, K = w.shape
+    _require(x.dim() == 2 and x.shape[1] == heads * K and x.stride(1) == 1 and w.is_contiguous()
+             and x.dtype in (w.dtype, torch.float32) and w.dtype in DTYPE_CODE,
+             "x [T, heads * K] in w's type or float32, and w [heads, N, K]")
+    _require(gate is None or (gate.dtype == torch.float32 and gate.dim() == 2 and gate.shape[0] == x.shape[0]
+                              and gate.shape[1] >= heads and gate.stride(1) == 1), "one float32 gate per token and head")
+    out = torch.empty((x.shape[0], heads * N), dtype=out_dtype or w.dtype, device=x.device)
+    _check(library().zb_head_linear(_ptr(out), _ptr(x), _ptr(w), _ptr(gate), x.stride(0), out.stride(0),
+                                    gate.stride(0) if gate is not None else 0, x.shape[0], heads, N, K,
+                                    DTYPE_CODE[x.dtype], DTYPE_CODE[w.dtype], DTYPE_CODE[out.dtype], _stream()),
+           "head_linear")
+    return out
+
+
+def route_max_outputs() -> int:
+    return library().zb_route_max_outputs()
+
+
+def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Token-choice routing: s = softmax(logits) over all outputs; the ``top`` outputs with the largest
+    s + correction are taken (ties: the lower index), each with the weight s.  Returns (ids int32 [T, top],
+    weights float32 [T, top]), in the order of choice."""
+    _cuda(logits, correction)
+    _require(logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1, "float32 logits [T, outputs]")
+    T, outputs = logits.shape
+    _f32_vector(correction, outputs, "the correction")
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    _check(library().zb_route(_ptr(ids), _ptr(weights), _ptr(logits), logits.stride(0), _ptr(correction), T, outputs,
+                              int(top), _stream()), "route")
+    return ids, weights
+
+
+def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                   w_down: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """sum_j weights[t, j] * expert_{ids[t, j]}(x[t]) for x [T, width]: expert e < E is
+    w_down[e] (act(w_gate[e] x) * (w_up[e] x)) with w_gate, w_up [E, ff, width] and w_down [E, width, ff]; an
+    id >= E names an identity expert, whose output is x itself.  Three launches over the tokens sorted
+    by expert (gate/up with the activation, down, the weighted sum); nothing comes back to the host."""
+    _cuda(x, ids, weights, w_gate, w_up, w_down)
+    T, width = x.shape
+    top = ids.shape[1]
+    E, ff, _ = w_gate.shape
+    _require(x.stride(1) == 1 and x.dtype in DTYPE_CODE and all(w.dtype == x.dtype and w.is_contiguous()
+             for w in (w_gate, w_up, w_down)), "tokens and expert matrices of one type")
+    _require(w_gate.shape == (E, ff, width) and w_up.shape == (E, ff, width) and w_down.shape == (E, width, ff),
+             "expert matrices [E, ff, width], [E, ff, width], [E, width, ff]")
+    _require(act in ACTIVATIONS, f"the gate's activation is one of {sorted(ACTIVATIONS)}")
+    _i32(ids)
+    _require(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == ids.shape, "one weight per choice")
+    lib, device = library(), x.device
+    num_slots = T * top
+    max_tiles = -(-num_slots // lib.zb_expert_tile_rows()) + E
+    plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=device)
+    slots = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
+    place = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
+    _check(lib.zb_route_align(_ptr(plan), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, max_tiles, _stream()),
+           "route_align")
+    hidden = torch.empty((max(num_slots, 1), ff), dtype=x.dtype, device=device)
+    y = torch.empty((max(num_slots, 1), width), dtype=torch.float32, device=device)
+    code = DTYPE_CODE[x.dtype]
+    _check(lib.zb_expert_product(_ptr(hidden), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slots),
+                                 max_tiles, ff, width, top, ACTIVATIONS[act], 0, code, _stream()), "expert_product")
+    _check(lib.zb_expert_product(_ptr(y), _ptr(hidden), ff, _ptr(w_down), None, _ptr(plan), _ptr(slots), max_tiles,
+                                 width, ff, top, ACTIVATIONS[act], 1, code, _stream()), "expert_product")
+    out = torch.empty((T, width), dtype=x.dtype, device=device)
+    _check(lib.zb_route_combine(_ptr(out), _ptr(y), _ptr(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(place), T,
+                                width, top, code, _stream()), "route_combine")
+    return out
 
 
 # ------------------------------------------------------------------------------ sampling

@@ -15,7 +15,11 @@ of another width than the keys (``value_dim``), a score scale of its own (``scal
 (``chunk`` = n: position i sees j <= i only if i // n == j // n, chunks counted from position 0), a
 learned sink per query head (``sinks``: exp(sink_h) joins the softmax's denominator, with no key, no
 value and no scaling), and the rotation of adjacent pairs on part of the head (position kind
-``rope_pairs``).  Any of these sends the layer down the general path: the projection's float32 output
+``rope_pairs``), values that are the keys as projected, before their norm (``values_from_keys``: there is
+no value projection), a per-head norm of q and k without scales (``unit_qk_norm``), a multiplier on the
+normed queries that grows with the position, 1 + coef * ln(floor((p + 1) / every) + 1) (``q_temp`` =
+{"coef", "every"}), and a smooth bound on the scaled scores, s <- softcap * tanh(s / softcap)
+(``softcap``).  Any of these sends the layer down the general path: the projection's float32 output
 goes through one kernel (bias, norms, rotation, cache write: ``ops.qkv_pairs``) and the general
 attention kernel, which takes all of them, for prompts and single tokens alike.
 """
@@ -46,7 +50,16 @@ class Attention(Mixer):
         self.nkv = int(p["num_kv_heads"])
         self.hd = int(p["head_dim"])
         self.window = int(p.get("window", 0))
-        self.eps = float(p["qk_norm_eps"]) if p.get("q_norm") else 0.0
+        self.unit_norm = bool(p.get("unit_qk_norm", False))
+        self.eps = float(p["qk_norm_eps"]) if (p.get("q_norm") or self.unit_norm) else 0.0
+        self.values_from_keys = bool(p.get("values_from_keys", False))
+        self.softcap = float(p.get("softcap") or 0.0)
+        temp = p.get("q_temp")
+        self.q_temp = (float(temp["coef"]), int(temp["every"])) if temp else None
+        if self.unit_norm and p.get("q_norm"):
+            raise ConfigError("a norm of q and k has scales or has none")
+        if self.softcap < 0.0 or (self.q_temp is not None and self.q_temp[1] <= 0):
+            raise ConfigError("softcap is not negative and q_temp.every is positive")
         self.dtype = dtype
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv != 0:
             raise ConfigError("attention needs positive head counts with heads divisible by kv_heads")
@@ -57,7 +70,10 @@ class Attention(Mixer):
         if self.vd <= 0 or self.vd > 256 or self.chunk < 0:
             raise ConfigError("attention takes value widths up to 256 and a chunk size that is not negative")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
-        self.w_qkv = torch.cat([weights[p["q_proj"]], weights[p["k_proj"]], weights[p["v_proj"]]], dim=0).contiguous()
+        if self.values_from_keys and self.vd != self.hd:
+            raise ConfigError("values that are the keys have the keys' width")
+        projections = ("q_proj", "k_proj") if self.values_from_keys else ("q_proj", "k_proj", "v_proj")
+        self.w_qkv = torch.cat([weights[p[name]] for name in projections], dim=0).contiguous()
         self.w_q = self.w_qkv[: self.nh * self.hd]
         self.w_o = weights[p["o_proj"]]
         self.q_norm = weights[p["q_norm"]] if p.get("q_norm") else None
@@ -69,7 +85,8 @@ class Attention(Mixer):
                 spec.position, dtype, device)
         else:
             self.position = None
-        biases = [weights[p[name]] if p.get(name) else None for name in ("q_bias", "k_bias", "v_bias")]
+        biases = [weights[p[name]] if p.get(name) else None
+                  for name in (("q_bias", "k_bias") if self.values_from_keys else ("q_bias", "k_bias", "v_bias"))]
         if any(b is not None for b in biases) and any(b is None for b in biases):
             raise ConfigError("q, k and v biases come together")
         self.qkv_bias = torch.cat([b.float() for b in biases]).contiguous() if biases[0] is not None else None
@@ -79,7 +96,8 @@ class Attention(Mixer):
         self.pair_freqs, self.pair_dims = pairs() if pairs is not None else (None, 0)
         # What only the general path takes.
         self.general = (pairs is not None or self.vd != self.hd or self.chunk > 0 or self.sinks is not None
-                        or self.qkv_bias is not None or self.o_bias is not None or p.get("scale") is not None)
+                        or self.qkv_bias is not None or self.o_bias is not None or p.get("scale") is not None
+                        or self.values_from_keys or self.unit_norm or self.softcap > 0.0 or self.q_temp is not None)
         if self.general:
             self._init_general(p)
             return
@@ -119,7 +137,7 @@ class Attention(Mixer):
         self.fused_position = False
         # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask and sinks
         # too, for keys and values of one width in bfloat16; everything else stays with the general kernel.
-        equal = self.vd == self.hd
+        equal = self.vd == self.hd and self.softcap == 0.0
         self.fast_decode = equal and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.fast_prefill = equal and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
@@ -135,15 +153,16 @@ class Attention(Mixer):
         decls = {
             p["q_proj"]: WeightDecl((nh * hd, hidden), ROLE_LINEAR),
             p["k_proj"]: WeightDecl((nkv * hd, hidden), ROLE_LINEAR),
-            p["v_proj"]: WeightDecl((nkv * vd, hidden), ROLE_LINEAR),
             p["o_proj"]: WeightDecl((hidden, nh * vd), ROLE_LINEAR),
         }
+        if not p.get("values_from_keys"):
+            decls[p["v_proj"]] = WeightDecl((nkv * vd, hidden), ROLE_LINEAR)
         if p.get("q_norm"):
             decls[p["q_norm"]] = WeightDecl((hd,), ROLE_NORM)
             decls[p["k_norm"]] = WeightDecl((hd,), ROLE_NORM)
         for name, size in (("q_bias", nh * hd), ("k_bias", nkv * hd), ("v_bias", nkv * vd), ("o_bias", hidden),
                            ("sinks", nh)):
-            if p.get(name):
+            if p.get(name) and not (name == "v_bias" and p.get("values_from_keys")):
                 decls[p[name]] = WeightDecl((size,), ROLE_ZERO)
         return decls
 
@@ -210,6 +229,7 @@ class Attention(Mixer):
         out = torch.empty((q.shape[0], self.nh * self.vd), dtype=q.dtype, device=q.device)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
         masks = {"chunk": self.chunk, "sinks": self.sinks} if (self.chunk or self.sinks is not None) else {}
+        general_only = {"softcap": self.softcap} if self.softcap > 0.0 else {}
         decode_done = self.fast_decode and ctx.num_decode_rows > 0
         if decode_done:
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
@@ -227,7 +247,8 @@ class Attention(Mixer):
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
-                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks)
+                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks,
+                                **general_only)
         return out
 
     takes_out_dtype = True
@@ -245,7 +266,8 @@ class Attention(Mixer):
         projected = ops.linear(x, weight, out_dtype=torch.float32)
         q = ops.qkv_pairs(projected, self.nh, self.nkv, self.hd, self.vd, bias, self.q_norm, self.k_norm, self.eps,
                           self.pair_freqs, self.pair_dims, ctx.positions, ctx.token_row, cache, table, ctx.status,
-                          self.dtype)
+                          self.dtype, unit_norm=self.unit_norm, values_from_keys=self.values_from_keys,
+                          q_temp=self.q_temp)
         attended = self.attend(q, ctx, call)
         return ops.linear(attended, self.w_o, out_dtype=out_dtype, bias=self.o_bias)
 

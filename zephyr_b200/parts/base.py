@@ -176,24 +176,36 @@ class DeferredSum:
     norm: "Norm"
     mult: float
 
-    def apply(self, hidden: torch.Tensor, then: "Norm | None" = None) -> torch.Tensor | None:
-        """Do the sum in place; with ``then`` return then(hidden) as well."""
+    def apply(self, hidden: torch.Tensor, then: "Norm | None" = None, rounded: torch.dtype | None = None):
+        """Do the sum in place; with ``then`` return then(hidden) as well; with ``rounded`` (and no
+        ``then``) return the sum in that type, for a part that reads the stream itself."""
         fused = getattr(self.norm, "add_scaled", None)
         if fused is not None and hidden.dtype == torch.float32 and (then is None or type(then) is type(self.norm)):
-            return fused(hidden, self.delta, self.mult, then)
+            if then is None and rounded is not None:
+                if rounded == hidden.dtype:
+                    fused(hidden, self.delta, self.mult)
+                    return hidden
+                if rounded == self.delta.dtype:
+                    return fused(hidden, self.delta, self.mult, None, rounded_sum=True)
+            else:
+                return fused(hidden, self.delta, self.mult, then)
         hidden.add_(self.norm.forward(self.delta).to(hidden.dtype), alpha=self.mult)
-        return then.forward(hidden) if then is not None else None
+        if then is not None:
+            return then.forward(hidden)
+        return hidden.to(rounded) if rounded is not None else None
 
 
 @dataclass
 class ResidualStream:
     """The hidden states between blocks: the stream itself and a summand not yet added, which the
     next norm adds in the same pass that normalises (``pending``: added as it is; ``deferred``: normed
-    and scaled first)."""
+    and scaled first).  ``rounded``: the stream's present value in the model's type, where whoever made
+    the stream had it at hand (an input part that writes both); it is void once anything is added."""
 
     hidden: torch.Tensor
     pending: torch.Tensor | None = None
     deferred: DeferredSum | None = None
+    rounded: torch.Tensor | None = None
 
     def flush(self) -> torch.Tensor:
         if self.pending is not None:
@@ -227,8 +239,9 @@ class InputPart(Part):
 
     def __init__(self, spec: InputSpec, weights: Mapping[str, torch.Tensor], dtype: torch.dtype): ...
 
-    def forward(self, ctx: StepContext) -> torch.Tensor:
-        """[T, hidden] in the model's type for the step's tokens (``ctx.token_ids``)."""
+    def forward(self, ctx: StepContext) -> "torch.Tensor | ResidualStream":
+        """[T, hidden] in the model's type for the step's tokens (``ctx.token_ids``), or a whole
+        ``ResidualStream`` (a float32 stream with its rounded copy)."""
         raise NotImplementedError
 
 

@@ -9,6 +9,10 @@ stream: r = x + m * mixer_out(mixer(mixer_norm(x))); x' = r + m * ffn_out(ffn(ff
 stream is float32.  The feed-forward may be missing; the layer is then its first half.  Each sum
 runs in the same kernel as the norm that follows it where the norms offer that (``Norm.add_scaled``),
 the last one as a ``DeferredSum`` that the next block or the output part takes up.
+
+``outnorm_residual``: a norm on each part's output only; the parts read the stream itself:
+r = x + mixer_out(mixer(x)); x' = r + ffn_out(ffn(r)).  The stream is float32; in a bfloat16 model the
+parts get its rounding, which the kernel that does a sum writes in the same pass.
 """
 
 from __future__ import annotations
@@ -83,5 +87,38 @@ class SandwichResidual(Block):
         return stream
 
 
+class OutputNormResidual(Block):
+    graph_safe = True
+    feed_forward_optional = True
+
+    norm_names = ("mixer_out", "feed_forward_out")
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, norms: Mapping[str, Norm], params=None):
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.norms = dict(norms)
+        self.dtype = norms["mixer_out"].dtype
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, call: LayerCall) -> ResidualStream:
+        if stream.pending is not None or stream.hidden.dtype != torch.float32:
+            stream.hidden, stream.rounded = stream.flush().float(), None
+        hidden = stream.hidden
+        if stream.deferred is not None:
+            x = stream.deferred.apply(hidden, rounded=self.dtype)
+            stream.deferred = None
+        elif stream.rounded is not None:
+            x = stream.rounded
+        else:
+            x = hidden if self.dtype == torch.float32 else hidden.to(self.dtype)
+        stream.rounded = None
+        summand = DeferredSum(self.mixer.forward(x, ctx, call), self.norms["mixer_out"], 1.0)
+        if self.feed_forward is not None:
+            x = summand.apply(hidden, rounded=self.dtype)
+            summand = DeferredSum(self.feed_forward.forward(x), self.norms["feed_forward_out"], 1.0)
+        stream.deferred = summand
+        return stream
+
+
 register_block("prenorm_residual", PreNormResidual)
+register_block("outnorm_residual", OutputNormResidual)
 register_block("sandwich_residual", SandwichResidual)

@@ -1,7 +1,7 @@
 """What lies before the first layer and after the last one, as parts.
 
-``embedding``: h[t, :] = E[id[t], :], no scaling (reference: src/layer/embedding.cpp:17-31,
-src/model/causal_lm/qwen3.cpp:122-123,169).
+``embedding``: h[t, :] = E[id[t], :] (reference: src/layer/embedding.cpp:17-31,
+src/model/causal_lm/qwen3.cpp:122-123,169), times ``scale`` where the spec gives one (float32 streams).
 
 ``norm_head``: the final norm and the vocabulary projection without bias, for the wanted tokens only
 (reference: src/model/causal_lm/qwen3.cpp:133-136,173-180).  The norm is row-wise, so it runs on
@@ -16,6 +16,7 @@ from typing import Mapping
 
 import torch
 
+from ..config.errors import ConfigError
 from ..config.spec import InputSpec, OutputSpec
 from ..kernels import ops
 from ..weights.loader import ROLE_EMBEDDING, ROLE_LINEAR, WeightDecl
@@ -29,6 +30,11 @@ class Embedding(InputPart):
         self.table = weights[spec.params["weight"]]
         # A model whose residual stream is float32 takes the table's rows as float32 from the start.
         self.float32_stream = bool(spec.params.get("float32_stream", False))
+        self.scale = float(spec.params.get("scale", 1.0))
+        # For models whose first part reads the stream itself: hand on its rounding with it.
+        self.rounded_copy = bool(spec.params.get("rounded_copy", False))
+        if self.scale != 1.0 and not self.float32_stream:
+            raise ConfigError("an embedding multiplier comes with a float32 stream")
 
     @staticmethod
     def weight_decls(spec: InputSpec) -> dict[str, WeightDecl]:
@@ -39,6 +45,12 @@ class Embedding(InputPart):
         return []          # a step gathers a few rows of the table; it does not stream it
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
+        if self.float32_stream and (self.scale != 1.0 or self.rounded_copy):
+            # The stream, and its rounding for the first part that reads the stream itself.
+            if self.table.dtype == torch.float32:
+                return ops.embedding_f32(self.table, ctx.token_ids, ctx.status, self.scale)
+            hidden, rounded = ops.embedding_f32(self.table, ctx.token_ids, ctx.status, self.scale, rounded=True)
+            return ResidualStream(hidden, rounded=rounded)
         if self.float32_stream:
             return ops.embedding_f32(self.table, ctx.token_ids, ctx.status)
         return ops.embedding(self.table, ctx.token_ids, ctx.status)

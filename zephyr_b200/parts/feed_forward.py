@@ -1,4 +1,5 @@
-"""The dense SwiGLU feed-forward: down(silu(gate(x)) * up(x)), no biases.
+"""The dense gated feed-forward: down(act(gate(x)) * up(x)), no biases; act is SiLU (SwiGLU) unless
+the spec's ``activation`` says "relu".
 
 Gate and up run as one product over one packed weight [2I, H], as the reference packs them at
 load (src/layer/mlp.cpp:16-36); the reference puts all gate rows first, this part alternates blocks
@@ -12,6 +13,7 @@ from typing import Mapping
 
 import torch
 
+from ..config.errors import ConfigError
 from ..config.spec import FeedForwardSpec
 from ..kernels import ops
 from ..weights.loader import ROLE_LINEAR, WeightDecl
@@ -25,6 +27,9 @@ class SwiGLU(FeedForward):
         p = spec.params
         self.hidden = int(p["hidden_size"])
         self.intermediate = int(p["intermediate_size"])
+        self.activation = str(p.get("activation", "silu"))
+        if self.activation not in ops.ACTIVATIONS:
+            raise ConfigError(f"a gated feed-forward's activation is one of {sorted(ops.ACTIVATIONS)}")
         gate, up = weights[p["gate_proj"]], weights[p["up_proj"]]
         # With I a multiple of 8 the rows alternate in blocks of 8 gate rows and their 8 up rows, the
         # order in which the decode kernel applies silu(gate) * up inside the product's epilogue.
@@ -47,9 +52,12 @@ class SwiGLU(FeedForward):
         }
 
     def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
-        return (self.w_gate_up, self.w_down) if self.blocked else None
+        return (self.w_gate_up, self.w_down) if self.blocked and self.activation == "silu" else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.activation != "silu":      # the products with the activation inside are SiLU's
+            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked, act=self.activation)
+            return ops.linear(hidden, self.w_down)
         if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
             hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True)       # product and activation in one kernel
         elif (self.blocked and (x.shape[0] >= ops.GEMM_TC_MIN_ROWS or not ops.USE_LIBRARY_PRODUCTS)
@@ -61,3 +69,4 @@ class SwiGLU(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("gated", SwiGLU)        # the same part under the name that fits any activation

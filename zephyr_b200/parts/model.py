@@ -212,6 +212,11 @@ class Model:
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Run the step's tokens through the model; float32 logits [wanted, vocab]."""
         hidden = self.input.forward(ctx)
+        if isinstance(hidden, ResidualStream):
+            stream = hidden
+            for call in self.spec.run_order:
+                stream = self.layers[call.layer].forward(stream, ctx, call)
+            return self.output.forward(stream, ctx)
         if self.use_chains and self.chains is not None and self.chains.supports(ctx.num_tokens):
             first = self._lane_split(ctx)
             if first:

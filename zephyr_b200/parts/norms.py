@@ -2,7 +2,7 @@
 the normalisation and not as (1 + w) (reference: src/layer/normalization.cpp:10-18,
 deps/ttl/src/kernels/normalization/normalization.cu:76-139).
 
-LayerNorm: mean and variance of the row, scale and shift."""
+LayerNorm: mean and variance of the row, a scale and (where the spec names one) a shift."""
 
 from __future__ import annotations
 
@@ -12,7 +12,6 @@ import torch
 
 from ..config.spec import NormSpec
 from ..kernels import ops
-from ..config.errors import ConfigError
 from ..weights.loader import ROLE_NORM, ROLE_ZERO, WeightDecl
 from .base import Norm, register_norm
 
@@ -52,22 +51,25 @@ class LayerNorm(Norm):
         self.eps = float(spec.eps)
         self.dtype = dtype
         self.weight = weights[spec.weight].float().contiguous()
-        self.bias = weights[spec.bias].float().contiguous()
+        self.bias = weights[spec.bias].float().contiguous() if spec.bias is not None else None
 
     @staticmethod
     def weight_decls(spec: NormSpec) -> dict[str, WeightDecl]:
-        if spec.bias is None:
-            raise ConfigError("a layer norm needs the name of its shift")
-        return {spec.weight: WeightDecl((spec.size,), ROLE_NORM), spec.bias: WeightDecl((spec.size,), ROLE_ZERO)}
+        decls = {spec.weight: WeightDecl((spec.size,), ROLE_NORM)}
+        if spec.bias is not None:           # a spec without the name of a shift: scale only
+            decls[spec.bias] = WeightDecl((spec.size,), ROLE_ZERO)
+        return decls
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.layer_norm(x, self.weight, self.bias, self.eps, out_dtype=self.dtype)
 
     def add_scaled(self, residual: torch.Tensor, delta: torch.Tensor, mult: float,
-                   then: "LayerNorm | None" = None) -> torch.Tensor | None:
-        """residual (float32) += mult * norm(delta), in place; with ``then`` also returns then(residual)."""
+                   then: "LayerNorm | None" = None, rounded_sum: bool = False) -> torch.Tensor | None:
+        """residual (float32) += mult * norm(delta), in place; with ``then`` also returns then(residual),
+        with ``rounded_sum`` the sum itself in delta's type."""
         if then is None:
-            return ops.residual_layer_norm(residual, delta, self.weight, self.bias, self.eps, mult)
+            return ops.residual_layer_norm(residual, delta, self.weight, self.bias, self.eps, mult,
+                                           rounded_sum=rounded_sum)
         return ops.residual_layer_norm(residual, delta, self.weight, self.bias, self.eps, mult,
                                        then.weight, then.bias, then.eps)
 
