@@ -93,30 +93,46 @@ def dense_ff(h: torch.Tensor, w: dict, prefix: str) -> torch.Tensor:
     return (torch.relu(h @ w[f"{prefix}.gate"].T) * (h @ w[f"{prefix}.up"].T)) @ w[f"{prefix}.down"].T
 
 
-def routed_ff(h: torch.Tensor, w: dict, prefix: str, mlp: dict) -> torch.Tensor:
+def routing(z: torch.Tensor, correction: torch.Tensor, top: int):
+    """Router logits z [T, outputs] -> (chosen outputs [T][top], their weights, the margin of every token's
+    choice: how far the last chosen output's choice score lies above the best one left out)."""
+    s = torch.softmax(z, dim=-1)
+    choice = s + correction
+    chosen, weights, margins = [], [], []
+    for t in range(z.shape[0]):
+        order = sorted(range(z.shape[1]), key=lambda e: (-float(choice[t, e]), e))
+        chosen.append(order[:top])
+        weights.append([float(s[t, e]) for e in order[:top]])
+        margins.append(float(choice[t, order[top - 1]] - choice[t, order[top]]) if top < z.shape[1] else float("inf"))
+    return chosen, weights, margins
+
+
+def routed_ff(h: torch.Tensor, w: dict, prefix: str, mlp: dict, margins: list | None = None) -> torch.Tensor:
     r = mlp["router"]
-    real, identity, top = r["experts"], r.get("identity", 0), r["top"]
-    s = torch.softmax(h @ w[f"{prefix}.router"].T, dim=-1)    # over real + identity outputs
-    choice = s + w[f"{prefix}.correction"]
+    real, top = r["experts"], r["top"]
+    chosen, weights, gaps = routing(h @ w[f"{prefix}.router"].T, w[f"{prefix}.correction"], top)
+    if margins is not None:
+        margins.append(gaps)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        order = sorted(range(real + identity), key=lambda e: (-float(choice[t, e]), e))[:top]
-        for e in order:
+        for e, weight in zip(chosen[t], weights[t]):
             if e >= real:
                 y = h[t]
             else:
                 p = f"{prefix}.e{e}"
                 gate = h[t] @ w[f"{p}.gate"].T
                 y = (gate * torch.sigmoid(gate) * (h[t] @ w[f"{p}.up"].T)) @ w[f"{p}.down"].T
-            out[t] += s[t, e] * y
+            out[t] += weight * y
     return out
 
 
-def forward(config: dict, weights: dict, tokens: list[int], layer_outputs: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence, float64.  ``layer_outputs`` collects the stream after each layer."""
+def forward(config: dict, weights: dict, tokens: list[int], layer_outputs: list | None = None,
+            margins: list | None = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence, float64.  ``layer_outputs`` collects the stream after each layer,
+    ``margins`` one list per routed layer with every token's routing margin."""
     w = {name: t.to(F64) for name, t in weights.items()}
     eps = float(config["norm"]["eps"])
-    x = w["embed"][torch.tensor(tokens)] * config["embedding"]["scale"]
+    x = w["embed"][torch.tensor(tokens)] * config.get("embedding", {}).get("scale", 1.0)
     for i, layer in enumerate(config["layers"]):
         m = layer["mixer"]
         if layer["type"] == "latent_attention":
@@ -126,7 +142,7 @@ def forward(config: dict, weights: dict, tokens: list[int], layer_outputs: list 
         x = x + layer_norm_scale(mixed, w[f"l{i}.norm1"], eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = dense_ff(x, w, f"l{i}.mlp") if mlp["kind"] == "dense" else routed_ff(x, w, f"l{i}.mlp", mlp)
+            y = dense_ff(x, w, f"l{i}.mlp") if mlp["kind"] == "dense" else routed_ff(x, w, f"l{i}.mlp", mlp, margins)
             x = x + layer_norm_scale(y, w[f"l{i}.norm2"], eps)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())

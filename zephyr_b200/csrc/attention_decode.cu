@@ -64,6 +64,9 @@ struct DecodeArgs {
   int chunk;                     // n > 0: the query (at position ctx_total - 1) sees only keys >= its position / n * n
   const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
   float scale_log2;              // scale * log2(e)
+  float softcap_log2;            // > 0: scores are softcap * tanh(scale * s / softcap); this is softcap * log2(e)
+  float scale_over_cap;          // scale / softcap
+  int keys_only;                 // a page holds keys alone, [nkv][page_size][hd], and they are the values too
   int* status;
   // Position encoding inside this kernel (`qkv` null: off; q then holds finished queries and the
   // cache the newest keys and values).  With it, q is not read: a request's new token lies raw in
@@ -462,7 +465,7 @@ paged_decode_kernel(const DecodeArgs a) {
   // Balanced items: as many tiles per range as spread all tiles evenly over the CTAs.
   const int per_range = a.split_size == 0 ? max(1, (prefix[a.n_rows] + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) : 0;
   const int page_size = 1 << a.page_shift;
-  const long long page_stride = 2LL * a.nkv * page_size * HD;
+  const long long page_stride = (a.keys_only ? 1LL : 2LL) * a.nkv * page_size * HD;
   const bool fused = a.qkv != nullptr;       // the new tokens' position encoding happens in this kernel
 
   if (warp >= DEC_CONSUMERS) {
@@ -565,7 +568,7 @@ paged_decode_kernel(const DecodeArgs a) {
         page_ids[i] = first_block + i < a.max_blocks ? table[first_block + i] : -1;
       __syncwarp();
       const __nv_bfloat16* base = a.kv_cache + static_cast<long long>(it.kvh) * page_size * HD;
-      const long long v_offset = static_cast<long long>(a.nkv) * page_size * HD;
+      const long long v_offset = a.keys_only ? 0LL : static_cast<long long>(a.nkv) * page_size * HD;
       // A tile's rows are copied in runs that are contiguous in the cache: a whole page at a time for
       // pages of up to 32 positions, a 32-row piece of a page for larger ones.  One bulk copy for
       // the keys of a run and one for its values: a handful of instructions move 16 KB.
@@ -707,7 +710,9 @@ paged_decode_kernel(const DecodeArgs a) {
         for (int c = 0; c < 4; ++c) {
           const int pos = key0 + nt * 8 + quad_col + (c & 1);
           const bool valid = pos >= it.begin && pos < it.end;
-          s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
+          const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[nt][c] * a.scale_over_cap)
+                                                     : s[nt][c] * a.scale_log2;
+          s[nt][c] = valid ? scaled : -INFINITY;
           tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
         }
       }
@@ -989,9 +994,10 @@ static int paged_decode_entry(void* out, const void* q, const void* kv_cache, co
                               int page_size, int num_pages, int num_rows, const int* rows, int n_rows,
                               const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd, int window,
                               float scale, int split_size, int max_splits, float* scratch, int* counters, int* status,
-                              const DecodeFusion* fusion, void* stream, int chunk = 0, const float* sinks = nullptr) {
+                              const DecodeFusion* fusion, void* stream, int chunk = 0, const float* sinks = nullptr,
+                              float softcap = 0.0f, int keys_only = 0) {
   if (n_rows < 0 || max_splits <= 0 || split_size < 0 || split_size % DEC_TILE != 0 || page_size <= 0 || window < 0 ||
-      chunk < 0 || counters == nullptr)
+      chunk < 0 || counters == nullptr || softcap < 0.0f || (keys_only && fusion != nullptr))
     return ERR_BAD_ARGUMENT;
   if (!zb_paged_decode_supported(nh, nkv, hd, DTYPE_BF16) || (page_size & (page_size - 1)) != 0) return ERR_UNSUPPORTED;
   if (n_rows == 0) return OK;
@@ -1036,6 +1042,9 @@ static int paged_decode_entry(void* out, const void* q, const void* kv_cache, co
   }
   a.ring_slots = 0;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.softcap_log2 = softcap * 1.4426950408889634f;
+  a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  a.keys_only = keys_only;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   switch (hd) {
@@ -1056,15 +1065,17 @@ ZB_API int zb_paged_decode(void* out, const void* q, const void* kv_cache, const
                             status, nullptr, stream);
 }
 
-// The same with a chunked mask and sinks, as in the general kernel (attention_simt.cu).
+// The same with a chunked mask, sinks, a smooth bound on the scores and a cache of keys that are the values
+// too, as in the general kernel (attention_simt.cu).
 ZB_API int zb_paged_decode_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
                                   int max_blocks, int page_size, int num_pages, int num_rows, const int* rows,
                                   int n_rows, const int* row_q_start, const int* row_ctx, int nh, int nkv, int hd,
-                                  int window, int chunk, float scale, const float* sinks, int split_size,
-                                  int max_splits, float* scratch, int* counters, int* status, void* stream) {
+                                  int window, int chunk, float scale, float softcap, int keys_only,
+                                  const float* sinks, int split_size, int max_splits, float* scratch, int* counters,
+                                  int* status, void* stream) {
   return paged_decode_entry(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, rows, n_rows,
                             row_q_start, row_ctx, nh, nkv, hd, window, scale, split_size, max_splits, scratch, counters,
-                            status, nullptr, stream, chunk, sinks);
+                            status, nullptr, stream, chunk, sinks, softcap, keys_only);
 }
 
 // The same with the new tokens' position encoding inside the kernel: `qkv` [T, qkv_stride] holds each

@@ -35,6 +35,9 @@ struct PrefillArgs {
   int chunk;                     // n > 0: a query at position p sees only keys >= (p / n) * n
   const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
   float scale_log2;
+  float softcap_log2;            // > 0: scores are softcap * tanh(scale * s / softcap); this is softcap * log2(e)
+  float scale_over_cap;          // scale / softcap
+  int keys_only;                 // a page holds keys alone, [nkv][page_size][hd], and they are the values too
   int* status;
 };
 
@@ -95,12 +98,12 @@ paged_prefill_kernel(const PrefillArgs a) {
           ok = false;
         } else {
           // logical chunk c / 8 of the row sits at the permuted chunk (common.cuh: kv_swizzle)
-          src += ((static_cast<long long>(page) * 2 * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD +
+          src += ((static_cast<long long>(page) * (a.keys_only ? 1 : 2) * a.nkv + kvh) * a.page_size + pos % a.page_size) * HD +
                  (((c >> 3) ^ kv_swizzle(pos, CHUNKS)) << 3);
         }
       }
       cp_async_16(ks + j * KROW + c, src, ok);
-      cp_async_16(vs + j * KROW + c, ok ? src + static_cast<long long>(a.nkv) * a.page_size * HD : src, ok);
+      cp_async_16(vs + j * KROW + c, ok && !a.keys_only ? src + static_cast<long long>(a.nkv) * a.page_size * HD : src, ok);
     }
   };
   load_tile(0);
@@ -157,7 +160,9 @@ paged_prefill_kernel(const PrefillArgs a) {
         const int pos = k0 + nt * 8 + quad_col + (c & 1);
         const int qp = qpos[c >> 1];
         const bool valid = pos <= qp && pos >= lo && (a.window == 0 || pos > qp - a.window) && pos >= chunk_start[c >> 1];
-        s[nt][c] = valid ? s[nt][c] * a.scale_log2 : -INFINITY;
+        const float scaled = a.softcap_log2 > 0.0f ? a.softcap_log2 * tanhf(s[nt][c] * a.scale_over_cap)
+                                                   : s[nt][c] * a.scale_log2;
+        s[nt][c] = valid ? scaled : -INFINITY;
         tile_max[c >> 1] = fmaxf(tile_max[c >> 1], s[nt][c]);
       }
     }
@@ -252,8 +257,8 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
                                    int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
                                    const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
                                    const int* row_ctx, int nh, int nkv, int hd, int window, int chunk, float scale,
-                                   const float* sinks, int* status, void* stream) {
-  if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0) return ERR_BAD_ARGUMENT;
+                                   float softcap, int keys_only, const float* sinks, int* status, void* stream) {
+  if (n_tiles < 0 || page_size <= 0 || window < 0 || chunk < 0 || softcap < 0.0f) return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_supported(nh, nkv, hd, DTYPE_BF16)) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   if (n_tiles > 65535) return ERR_UNSUPPORTED;
@@ -266,6 +271,9 @@ ZB_API int zb_paged_prefill_masked(void* out, const void* q, const void* kv_cach
   a.max_blocks = max_blocks; a.page_size = page_size; a.num_pages = num_pages; a.num_rows = num_rows;
   a.nh = nh; a.nkv = nkv; a.window = window; a.chunk = chunk; a.sinks = sinks;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.softcap_log2 = softcap * 1.4426950408889634f;
+  a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  a.keys_only = keys_only;
   a.status = status;
   auto s = static_cast<cudaStream_t>(stream);
   switch (hd) {
@@ -281,6 +289,6 @@ ZB_API int zb_paged_prefill(void* out, const void* q, const void* kv_cache, cons
                             int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
                             int nkv, int hd, int window, float scale, int* status, void* stream) {
   return zb_paged_prefill_masked(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, tile_row,
-                                 tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, 0, scale,
+                                 tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, 0, scale, 0.0f, 0,
                                  nullptr, status, stream);
 }

@@ -33,6 +33,7 @@ struct SmallGemmArgs {
   const __nv_bfloat16* w;
   int M, N, K;
   long long ldx, ldw, ldy;
+  int relu_gate;      // with the gated epilogue: max(gate, 0) * up instead of silu(gate) * up
 };
 
 __device__ __forceinline__ uint4 load16_or_zero(const __nv_bfloat16* p, bool ok) {
@@ -123,7 +124,8 @@ gemm_small_kernel(const SmallGemmArgs a) {
           }
         const int token = mt * 8 + tok, col = blockIdx.x * 8 + r;
         if (token < a.M && n0 + r + 8 < a.N)
-          store_out<TOut>(y + static_cast<size_t>(token) * a.ldy + col, gate / (1.0f + expf(-gate)) * up);
+          store_out<TOut>(y + static_cast<size_t>(token) * a.ldy + col,
+                          (a.relu_gate ? fmaxf(gate, 0.0f) : gate / (1.0f + expf(-gate))) * up);
       }
     } else {
       for (int e = threadIdx.x; e < PER_WARP; e += GS_WARPS * 32) {
@@ -187,7 +189,7 @@ ZB_API int zb_gemm_small_ksplit(int N, int K) {
   return ksplit;
 }
 
-// y = x w^T (swiglu = 0), or y[:, 8j + r] = silu(x w[16j + r]^T) * (x w[16j + 8 + r]^T) (swiglu = 1;
+// y = x w^T (swiglu = 0), or y[:, 8j + r] = silu(x w[16j + r]^T) * (x w[16j + 8 + r]^T) (swiglu = 1; 2: max(., 0) for silu;
 // w holds gate and up rows interleaved in blocks of 8, y has N / 2 columns).
 // x: [M, K] bfloat16 rows ldx apart (ldx, ldw multiples of 8, pointers 16-byte aligned);
 // out_dtype: bfloat16 or float32.
@@ -202,6 +204,7 @@ ZB_API int zb_gemm_small(void* y, const void* x, const void* w, int M, int N, in
   a.x = static_cast<const __nv_bfloat16*>(x);
   a.w = static_cast<const __nv_bfloat16*>(w);
   a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldw = ldw; a.ldy = ldy;
+  a.relu_gate = swiglu == 2;
   const int ksplit = zb_gemm_small_ksplit(N, K);
   auto s = static_cast<cudaStream_t>(stream);
   if (swiglu)

@@ -38,6 +38,7 @@ constexpr int GT_THREADS = 192;
 constexpr int GT_WAIT_LIMIT = 1 << 18;
 constexpr int GT_PAIR = 2;                 // as block_n: tiles of 256 x 256 on pairs of SMs
 constexpr int GT_EPI_PLAIN = 0;
+constexpr int GT_EPI_RELU_GATE = 3;        // the interface's code for the gated epilogue with max(gate, 0) in SiLU's place
 constexpr int GT_EPI_SWIGLU = 1;           // columns 16 j .. 16 j + 7 are gates, 16 j + 8 .. 16 j + 15 their ups
 constexpr int GT_EPI_FLOAT = 2;            // the sums as they are, float32 (logits)
 constexpr int GT_A_BYTES = GT_BM * GT_BK * 2;
@@ -57,6 +58,7 @@ struct GemmTcArgs {
   CUtensorMap y_map;             // y as [M][N, or N / 2 with the activation]; box 64 x 32; rows and columns beyond are not written
   int M, N, K;
   int tiles_m, tiles;
+  int relu_gate;                 // with the gated epilogue: max(gate, 0) * up instead of silu(gate) * up
   int* status;
 };
 
@@ -104,7 +106,7 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 // what lies beyond the matrix.
 template <int BN, int EPI>
 __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigned tmem_row, int row0, int n0, int width,
-                                               unsigned char* staging, int& stores, int lane) {
+                                               unsigned char* staging, int& stores, int lane, int relu_gate) {
   // A group = 128 bytes of a row's output: 64 bfloat16 columns from two reads of 32 sums (four reads with
   // the activation, which halves them), or 32 float32 columns from one read.
   constexpr int READS = EPI == GT_EPI_SWIGLU ? 4 : EPI == GT_EPI_FLOAT ? 1 : 2;
@@ -137,7 +139,7 @@ __device__ __forceinline__ void write_out_rows(const CUtensorMap& y_map, unsigne
           for (int i = 0; i < 8; ++i) {
             if (EPI == GT_EPI_SWIGLU) {
               const float gate = __uint_as_float(v[16 * j + i]), up = __uint_as_float(v[16 * j + 8 + i]);
-              o[i] = silu_fast(gate) * up;
+              o[i] = (relu_gate ? fmaxf(gate, 0.0f) : silu_fast(gate)) * up;
             } else {
               o[i] = __uint_as_float(v[8 * j + i]);
             }
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
       }
       tc_fence_after_sync();
       write_out_rows<BN, EPI>(a.y_map, tmem_base + (static_cast<unsigned>(32 * quarter) << 16) + acc * BN,
-                              m0 + 32 * quarter, n0, width, staging, stores, lane);
+                              m0 + 32 * quarter, n0, width, staging, stores, lane, a.relu_gate);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc_mbar_arrive(&sh.acc_empty[acc]);
@@ -456,7 +458,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GT_THREADS, 1) gemm_
       }
       tc_fence_after_sync();
       write_out_rows<GP_BN, EPI>(a.y_map, tmem_base + (static_cast<unsigned>(32 * quarter) << 16) + acc * GP_BN,
-                                 m0 + 32 * quarter, n0, width, staging, stores, lane);
+                                 m0 + 32 * quarter, n0, width, staging, stores, lane, a.relu_gate);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_in_cluster(in_cta_of_rank(smem_u32(&sh.acc_empty[acc]), 0));
@@ -546,6 +548,7 @@ using namespace zb;
 
 // 1 if zb_gemm_tc takes these sizes (x [M, K] with ldx elements between rows, w [N, K], y with ldy).
 ZB_API int zb_gemm_tc_supported(int M, int N, int K, long long ldx, int ldy, int epilogue) {
+  if (epilogue == GT_EPI_RELU_GATE) epilogue = GT_EPI_SWIGLU;
   if (M <= 0 || N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K || (epilogue != GT_EPI_FLOAT && ldy % 8 != 0)) return 0;
   if (epilogue == GT_EPI_SWIGLU) return N % 16 == 0 && ldy >= N / 2;
   if (epilogue == GT_EPI_FLOAT) return ldy % 4 == 0 && ldy >= N;          // ldy counts float32 elements then
@@ -554,11 +557,13 @@ ZB_API int zb_gemm_tc_supported(int M, int N, int K, long long ldx, int ldy, int
 
 // y = epilogue(x w^T), x and w bfloat16.  epilogue 0: y [M, N] bfloat16; 2: the same in float32;
 // 1: y [M, N / 2] = silu(gate) * up for w's rows in
-// blocks of 8 gate rows and their 8 up rows.  block_n is 256 or 128, or 2 for tiles of 256 x 256 on pairs of
+// blocks of 8 gate rows and their 8 up rows; 3: the same with max(gate, 0) * up.  block_n is 256 or 128, or 2 for tiles of 256 x 256 on pairs of
 // SMs (0: chosen from the sizes).
 ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K, long long ldx, int ldy, int epilogue,
                       int block_n, int* status, void* stream) {
   if (!zb_gemm_tc_supported(M, N, K, ldx, ldy, epilogue)) return ERR_UNSUPPORTED;
+  const int relu_gate = epilogue == GT_EPI_RELU_GATE;
+  if (relu_gate) epilogue = GT_EPI_SWIGLU;
   if (reinterpret_cast<uintptr_t>(y) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
       reinterpret_cast<uintptr_t>(w) % 16 != 0)
     return ERR_BAD_ARGUMENT;
@@ -576,6 +581,7 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   if (block_n != 256 && block_n != 128 && block_n != GT_PAIR) return ERR_BAD_ARGUMENT;
   GemmTcArgs a;
   a.M = M; a.N = N; a.K = K;
+  a.relu_gate = relu_gate;
   a.status = status;
   if (!matrix_tensor_map(x, M, K, ldx, GT_BM, &a.x_map)) return ERR_CUDA;
   if (!matrix_tensor_map(y, M, epilogue == GT_EPI_SWIGLU ? N / 2 : N, ldy, 32, &a.y_map, epilogue == GT_EPI_FLOAT ? 4 : 2)) return ERR_CUDA;

@@ -7,8 +7,10 @@
 // attention's result, a weighted sum of latents per head, is carried out of it by the head's value map.
 //
 // float32 sums in the order of k; W and y in the model's type (y may be float32), x in that type or in
-// float32 (a projection that was left unrounded).
+// float32 (a projection that was left unrounded).  float32 matrices run on CUDA cores, bfloat16 ones on
+// the tensor cores (x rounded to bfloat16 as it is staged).
 #include "tile_product.cuh"
+#include "tile_product_mma.cuh"
 
 namespace zb {
 
@@ -49,6 +51,34 @@ __global__ void __launch_bounds__(TP_THREADS) head_linear_kernel(const HeadLinea
   }
 }
 
+template <typename X, typename OUT>
+__global__ void __launch_bounds__(TM_THREADS) head_linear_mma_kernel(const HeadLinearArgs a, int a_vectors, int w_vectors) {
+  __shared__ TileMmaSmem sm;
+  const int t0 = blockIdx.x * TM_BM, n0 = blockIdx.y * TM_BN, head = blockIdx.z;
+  if (threadIdx.x < TM_BM) {
+    const int t = t0 + threadIdx.x;
+    sm.row[threadIdx.x] = t < a.tokens ? static_cast<const X*>(a.x) + t * a.x_stride + static_cast<long long>(head) * a.K
+                                       : nullptr;
+  }
+  __syncthreads();
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(a.w) + (static_cast<size_t>(head) * a.N + n0) * a.K;
+  float acc[2][4][4];
+  tile_product_mma<false, X>(sm, w, nullptr, a.N - n0, a.K, a_vectors != 0, w_vectors != 0, acc);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int t = t0 + tm_row(c);
+    if (t >= a.tokens) continue;
+    float mult = 1.0f;
+    if (a.gate != nullptr) mult = 1.0f / (1.0f + expf(-a.gate[t * a.gate_stride + head]));
+    OUT* dst = static_cast<OUT*>(a.y) + t * a.y_stride + static_cast<long long>(head) * a.N;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      const int n = n0 + tm_col(nt, c);
+      if (n < a.N) dst[n] = from_float<OUT>(acc[0][nt][c] * mult);
+    }
+  }
+}
+
 }  // namespace zb
 
 using namespace zb;
@@ -67,13 +97,18 @@ ZB_API int zb_head_linear(void* y, const void* x, const void* w, const float* ga
   if (dtype == DTYPE_F32) {
     if (out_dtype != DTYPE_F32 || x_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
     head_linear_kernel<float, float, float><<<grid, TP_THREADS, 0, s>>>(a);
-  } else if (x_dtype == DTYPE_F32) {
-    if (out_dtype == DTYPE_F32) head_linear_kernel<float, bf16, float><<<grid, TP_THREADS, 0, s>>>(a);
-    else head_linear_kernel<float, bf16, bf16><<<grid, TP_THREADS, 0, s>>>(a);
-  } else if (out_dtype == DTYPE_F32) {
-    head_linear_kernel<bf16, bf16, float><<<grid, TP_THREADS, 0, s>>>(a);
+    return launch_result();
+  }
+  const dim3 wide((tokens + TM_BM - 1) / TM_BM, (N + TM_BN - 1) / TM_BN, heads);
+  const int w_vectors = K % 8 == 0 && tm_aligned(w, 16);
+  if (x_dtype == DTYPE_F32) {
+    const int a_vectors = K % 8 == 0 && x_stride % 4 == 0 && tm_aligned(x, 16);
+    if (out_dtype == DTYPE_F32) head_linear_mma_kernel<float, float><<<wide, TM_THREADS, 0, s>>>(a, a_vectors, w_vectors);
+    else head_linear_mma_kernel<float, bf16><<<wide, TM_THREADS, 0, s>>>(a, a_vectors, w_vectors);
   } else {
-    head_linear_kernel<bf16, bf16, bf16><<<grid, TP_THREADS, 0, s>>>(a);
+    const int a_vectors = K % 8 == 0 && x_stride % 8 == 0 && tm_aligned(x, 16);
+    if (out_dtype == DTYPE_F32) head_linear_mma_kernel<bf16, float><<<wide, TM_THREADS, 0, s>>>(a, a_vectors, w_vectors);
+    else head_linear_mma_kernel<bf16, bf16><<<wide, TM_THREADS, 0, s>>>(a, a_vectors, w_vectors);
   }
   return launch_result();
 }

@@ -12,13 +12,14 @@
 // Four steps, all shapes fixed by the step's token count (nothing is read back by the host):
 //   route     one warp per token: softmax, choice, selection -> ids [T, top], weights [T, top]
 //   align     one CTA: the (token, choice) slots sorted by expert, every expert's run cut into tiles of
-//             TP_BM rows -> slot list, tile list
+//             32 (float32) or 64 (bfloat16) rows -> slot list, tile list
 //   products  one CTA per (tile, 64 outputs): gate and up together with the activation, then down,
 //             each row's sums in the order of k, so a token's result does not depend on what else
-//             was routed to its expert
+//             was routed to its expert; float32 on CUDA cores, bfloat16 on the tensor cores
 //   combine   out[t] = sum_j weight[t, j] * (expert output of slot (t, j), or x[t] for an identity
 //             expert), in float32 and in the order of j, rounded once.
 #include "tile_product.cuh"
+#include "tile_product_mma.cuh"
 
 namespace zb {
 
@@ -98,7 +99,8 @@ route_kernel(int* ids, float* weights, const float* logits, long long logits_str
 constexpr int ALIGN_THREADS = 1024;
 
 __global__ void __launch_bounds__(ALIGN_THREADS)
-align_kernel(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts, int max_tiles) {
+align_kernel(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts, int max_tiles,
+             int tile_rows) {
   extern __shared__ int align_smem[];
   int* count = align_smem;                 // [experts]
   int* start = count + experts;            // [experts + 1]
@@ -114,10 +116,10 @@ align_kernel(int* plan, int* slots, int* place_of_slot, const int* ids, int num_
     int at = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
       start[e] = at;
-      for (int r = 0; r < count[e] && tiles < max_tiles; r += TP_BM, ++tiles) {
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += tile_rows, ++tiles) {
         plan[1 + 3 * tiles] = e;
         plan[2 + 3 * tiles] = at + r;
-        plan[3 + 3 * tiles] = min(TP_BM, count[e] - r);
+        plan[3 + 3 * tiles] = min(tile_rows, count[e] - r);
       }
       at += count[e];
     }
@@ -216,6 +218,60 @@ __global__ void __launch_bounds__(TP_THREADS) expert_down_kernel(const ExpertPro
   }
 }
 
+// The same two products on the tensor cores (bfloat16): tiles of TM_BM rows.
+__global__ void __launch_bounds__(TM_THREADS) expert_gate_up_mma_kernel(const ExpertProductArgs a, int vectors) {
+  __shared__ TileMmaSmem sm;
+  using T = __nv_bfloat16;
+  const int tile = blockIdx.x;
+  if (tile >= a.plan[0]) return;
+  const int expert = a.plan[1 + 3 * tile], place0 = a.plan[2 + 3 * tile], rows = a.plan[3 + 3 * tile];
+  const int n0 = blockIdx.y * TM_BN;
+  if (threadIdx.x < TM_BM) {
+    const T* src = nullptr;
+    if (static_cast<int>(threadIdx.x) < rows)
+      src = static_cast<const T*>(a.x) + static_cast<long long>(a.slots[place0 + threadIdx.x] / a.top) * a.x_stride;
+    sm.row[threadIdx.x] = src;
+  }
+  __syncthreads();
+  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  float acc[2][4][4];
+  tile_product_mma<true, T>(sm, static_cast<const T*>(a.w0) + w_at, static_cast<const T*>(a.w1) + w_at, a.N - n0, a.K,
+                            vectors != 0, vectors != 0, acc);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = tm_row(c), n = n0 + tm_col(nt, c);
+      if (r < rows && n < a.N)
+        static_cast<T*>(a.out)[static_cast<size_t>(place0 + r) * a.N + n] =
+            from_float<T>(expert_act(to_float(from_float<T>(acc[0][nt][c])), a.act) * to_float(from_float<T>(acc[1][nt][c])));
+    }
+}
+
+__global__ void __launch_bounds__(TM_THREADS) expert_down_mma_kernel(const ExpertProductArgs a, int vectors) {
+  __shared__ TileMmaSmem sm;
+  using T = __nv_bfloat16;
+  const int tile = blockIdx.x;
+  if (tile >= a.plan[0]) return;
+  const int expert = a.plan[1 + 3 * tile], place0 = a.plan[2 + 3 * tile], rows = a.plan[3 + 3 * tile];
+  const int n0 = blockIdx.y * TM_BN;
+  if (threadIdx.x < TM_BM)
+    sm.row[threadIdx.x] = static_cast<int>(threadIdx.x) < rows
+                              ? static_cast<const T*>(a.x) + static_cast<long long>(place0 + threadIdx.x) * a.x_stride
+                              : nullptr;
+  __syncthreads();
+  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  float acc[2][4][4];
+  tile_product_mma<false, T>(sm, static_cast<const T*>(a.w0) + w_at, nullptr, a.N - n0, a.K, vectors != 0, vectors != 0, acc);
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = tm_row(c), n = n0 + tm_col(nt, c);
+      if (r < rows && n < a.N) static_cast<float*>(a.out)[static_cast<size_t>(place0 + r) * a.N + n] = acc[0][nt][c];
+    }
+}
+
 // -------------------------------------------------------------------------------------------- combine
 template <typename T>
 __global__ void combine_kernel(T* out, const float* y, const T* x, long long x_stride, const int* ids,
@@ -240,7 +296,7 @@ __global__ void combine_kernel(T* out, const float* y, const T* x, long long x_s
 using namespace zb;
 
 ZB_API int zb_route_max_outputs() { return 32 * ROUTE_PER_LANE; }
-ZB_API int zb_expert_tile_rows() { return TP_BM; }
+ZB_API int zb_expert_tile_rows(int dtype) { return dtype == DTYPE_F32 ? TP_BM : TM_BM; }
 
 ZB_API int zb_route(int* ids, float* weights, const float* logits, long long logits_stride, const float* correction,
                     int tokens, int outputs, int top, void* stream) {
@@ -253,12 +309,12 @@ ZB_API int zb_route(int* ids, float* weights, const float* logits, long long log
 }
 
 ZB_API int zb_route_align(int* plan, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts,
-                          int max_tiles, void* stream) {
-  if (num_slots < 0 || experts <= 0 || max_tiles < 0) return ERR_BAD_ARGUMENT;
+                          int max_tiles, int tile_rows, void* stream) {
+  if (num_slots < 0 || experts <= 0 || max_tiles < 0 || tile_rows <= 0) return ERR_BAD_ARGUMENT;
   const size_t smem = (3 * static_cast<size_t>(experts) + 1) * sizeof(int);
   if (smem > 48 * 1024) return ERR_UNSUPPORTED;
   align_kernel<<<1, ALIGN_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(plan, slots, place_of_slot, ids,
-                                                                                num_slots, experts, max_tiles);
+                                                                                num_slots, experts, max_tiles, tile_rows);
   return launch_result();
 }
 
@@ -271,15 +327,19 @@ ZB_API int zb_expert_product(void* out, const void* x, long long x_stride, const
   ExpertProductArgs a;
   a.out = out; a.x = x; a.w0 = w0; a.w1 = w1; a.plan = plan; a.slots = slots; a.x_stride = x_stride;
   a.N = N; a.K = K; a.top = top; a.act = act;
-  const dim3 grid(max_tiles, (N + TP_BN - 1) / TP_BN);
+  const dim3 grid(max_tiles, (N + TP_BN - 1) / TP_BN);       // both tile forms are 64 outputs wide
+  static_assert(TP_BN == TM_BN, "one grid for both forms");
   auto s = static_cast<cudaStream_t>(stream);
-  if (down) {
-    if (dtype == DTYPE_F32) expert_down_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
-    else expert_down_kernel<__nv_bfloat16><<<grid, TP_THREADS, 0, s>>>(a);
-  } else {
-    if (dtype == DTYPE_F32) expert_gate_up_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
-    else expert_gate_up_kernel<__nv_bfloat16><<<grid, TP_THREADS, 0, s>>>(a);
+  if (dtype == DTYPE_F32) {
+    if (down) expert_down_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
+    else expert_gate_up_kernel<float><<<grid, TP_THREADS, 0, s>>>(a);
+    return launch_result();
   }
+  // Vector loads where every row of x and of the matrices starts on a 16-byte boundary.
+  const int vectors = K % 8 == 0 && x_stride % 8 == 0 && tm_aligned(x, 16) && tm_aligned(w0, 16) &&
+                      (w1 == nullptr || tm_aligned(w1, 16));
+  if (down) expert_down_mma_kernel<<<grid, TM_THREADS, 0, s>>>(a, vectors);
+  else expert_gate_up_mma_kernel<<<grid, TM_THREADS, 0, s>>>(a, vectors);
   return launch_result();
 }
 

@@ -58,9 +58,9 @@ _SIGNATURES = {
     "zb_head_linear": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int, c_int, c_int,
                        c_int, c_int, c_int, c_int, c_void_p],
     "zb_route_max_outputs": [],
-    "zb_expert_tile_rows": [],
+    "zb_expert_tile_rows": [c_int],
     "zb_route": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
-    "zb_route_align": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_route_align": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_expert_product": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_void_p],
     "zb_route_combine": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -100,11 +100,11 @@ _SIGNATURES = {
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p],
     "zb_paged_decode_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
-                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int,
-                               c_void_p, c_void_p, c_void_p, c_void_p],
+                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
+                               c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "zb_paged_prefill_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                 c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                c_void_p, c_void_p, c_void_p],
+                                c_float, c_int, c_void_p, c_void_p, c_void_p],
     "zb_paged_decode_fused": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
@@ -827,9 +827,9 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
                  window: int, scale: float, status: torch.Tensor, out: torch.Tensor,
                  scratch: torch.Tensor | None = None, split_size: int | None = None,
                  counters: torch.Tensor | None = None, chunk: int = 0,
-                 sinks: torch.Tensor | None = None) -> torch.Tensor:
+                 sinks: torch.Tensor | None = None, softcap: float = 0.0, keys_only: bool = False) -> torch.Tensor:
     """Split-context attention for rows with one new token each; writes those tokens' rows of ``out``.
-    ``chunk`` and ``sinks`` as in ``paged_attention``.
+    ``chunk``, ``sinks`` and ``softcap`` as in ``paged_attention``; ``keys_only`` as its ``shared_kv``.
 
     ``max_context`` is at least the longest context of the rows, the new token included.  ``scratch``
     (float32, any contents) and ``counters`` (int32, zero) come from a process-wide workspace unless
@@ -838,7 +838,7 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
     _i32(block_table, rows, row_q_start, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
-    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
+    pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0, q.dtype) if keys_only else _check_cache(kv_cache, nkv, hd, q.dtype)
     n_rows = rows.numel()
     if split_size is None and n_rows * nkv * 4 <= _sm_count():
         # A handful of long rows: fixed splits keep every item inside one row (a CTA whose share
@@ -857,15 +857,15 @@ def paged_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Ten
              f"scratch must hold {need} floats")
     _require(counters.dtype == torch.int32 and counters.is_contiguous() and counters.numel() >= n_rows * nkv,
              f"counters must hold {n_rows * nkv} zeroed int32 values")
-    if chunk or sinks is not None:
+    if chunk or sinks is not None or softcap or keys_only:
         _cuda(sinks)
         _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
                  "one float32 sink per query head")
         _check(library().zb_paged_decode_masked(
             _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
             block_table.shape[0], _ptr(rows), n_rows, _ptr(row_q_start), _ptr(row_ctx), nh, nkv, hd, int(window),
-            int(chunk), float(scale), _ptr(sinks), int(split_size), max_splits, _ptr(scratch), _ptr(counters),
-            _ptr(status), _stream()), "paged_decode")
+            int(chunk), float(scale), float(softcap), int(keys_only), _ptr(sinks), int(split_size), max_splits,
+            _ptr(scratch), _ptr(counters), _ptr(status), _stream()), "paged_decode")
         return out
     _check(library().zb_paged_decode(
         _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
@@ -959,24 +959,26 @@ def paged_prefill_supported(nh: int, nkv: int, hd: int, dtype: torch.dtype) -> b
 def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, tile_row: torch.Tensor,
                   tile_q0: torch.Tensor, row_q_start: torch.Tensor, row_q_len: torch.Tensor, row_ctx: torch.Tensor,
                   nh: int, nkv: int, hd: int, window: int, scale: float, status: torch.Tensor,
-                  out: torch.Tensor, chunk: int = 0, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                  out: torch.Tensor, chunk: int = 0, sinks: torch.Tensor | None = None, softcap: float = 0.0,
+                  keys_only: bool = False) -> torch.Tensor:
     """Tensor-core attention for rows with several new tokens, cut into tiles of
-    ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk`` and ``sinks`` as in
-    ``paged_attention``; with either the mma.sync kernel runs, at every head size."""
+    ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk``, ``sinks`` and
+    ``softcap`` as in ``paged_attention``, ``keys_only`` as its ``shared_kv``; with any of them the mma.sync
+    kernel runs, at every head size."""
     _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out)
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
-    pages, page_size = _check_cache(kv_cache, nkv, hd, q.dtype)
-    if chunk or sinks is not None:
+    pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0, q.dtype) if keys_only else _check_cache(kv_cache, nkv, hd, q.dtype)
+    if chunk or sinks is not None or softcap or keys_only:
         _cuda(sinks)
         _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
                  "one float32 sink per query head")
         _check(library().zb_paged_prefill_masked(
             _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
             block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
-            _ptr(row_ctx), nh, nkv, hd, int(window), int(chunk), float(scale), _ptr(sinks), _ptr(status), _stream()),
-            "paged_prefill")
+            _ptr(row_ctx), nh, nkv, hd, int(window), int(chunk), float(scale), float(softcap), int(keys_only),
+            _ptr(sinks), _ptr(status), _stream()), "paged_prefill")
         return out
     # Head size 128 runs on tcgen05 with the accumulators in tensor memory; other sizes on mma.sync.
     tensor_memory = USE_TCGEN05_PREFILL and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype],
@@ -1020,7 +1022,7 @@ def gemm_small_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
-               swiglu: bool = False) -> torch.Tensor:
+               swiglu: bool = False, act: str = "silu") -> torch.Tensor:
     """x [M <= 64, K] times w [N, K] transposed, bfloat16, float32 accumulation, weights read once.
     With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up rows, and the
     result is silu(gate) * up, [M, N / 2]."""
@@ -1033,7 +1035,8 @@ def gemm_small(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None =
     _require(not swiglu or N % 16 == 0, "swiglu needs a multiple of 16 rows")
     out = torch.empty((M, N // 2 if swiglu else N), dtype=out_dtype, device=x.device)
     _check(library().zb_gemm_small(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-                                   DTYPE_CODE[out_dtype], int(swiglu), _stream()), "gemm_small")
+                                   DTYPE_CODE[out_dtype], (2 if act == "relu" else 1) if swiglu else 0, _stream()),
+           "gemm_small")
     return out
 
 
@@ -1054,7 +1057,7 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) ->
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int = 0,
-            status: torch.Tensor | None = None, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+            status: torch.Tensor | None = None, out_dtype: torch.dtype | None = None, act: str = "silu") -> torch.Tensor:
     """x [M, K] times w [N, K] transposed on tcgen05 tensor cores, bfloat16 with float32 sums in
     tensor memory; the result in bfloat16, or with ``out_dtype=torch.float32`` the sums as they are.
     With ``swiglu`` the rows of w are blocks of 8 gate rows each followed by its 8 up
@@ -1073,7 +1076,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, block_n: int
     out = torch.empty((M, ldy), dtype=torch.float32 if wide else torch.bfloat16, device=x.device)
     if status is None:
         status = device_status(x.device)
-    _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, 2 if wide else int(swiglu),
+    _require(act in ACTIVATIONS, f"the gate's activation is one of {sorted(ACTIVATIONS)}")
+    gated = 3 if act == "relu" else 1         # the kernel's codes for the two gated epilogues
+    _check(library().zb_gemm_tc(_ptr(out), _ptr(x), _ptr(w), M, N, K, x.stride(0), ldy, 2 if wide else (gated if swiglu else 0),
                                 int(block_n), _ptr(status), _stream()), "gemm_tc")
     return out if ldy == width else out[:, :width].contiguous()
 
@@ -1284,15 +1289,16 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
     _require(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == ids.shape, "one weight per choice")
     lib, device = library(), x.device
     num_slots = T * top
-    max_tiles = -(-num_slots // lib.zb_expert_tile_rows()) + E
+    code = DTYPE_CODE[x.dtype]
+    tile_rows = lib.zb_expert_tile_rows(code)          # CUDA-core tiles in float32, tensor-core tiles in bfloat16
+    max_tiles = -(-num_slots // tile_rows) + E
     plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=device)
     slots = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
     place = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
-    _check(lib.zb_route_align(_ptr(plan), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, max_tiles, _stream()),
-           "route_align")
+    _check(lib.zb_route_align(_ptr(plan), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, max_tiles, tile_rows,
+                              _stream()), "route_align")
     hidden = torch.empty((max(num_slots, 1), ff), dtype=x.dtype, device=device)
     y = torch.empty((max(num_slots, 1), width), dtype=torch.float32, device=device)
-    code = DTYPE_CODE[x.dtype]
     _check(lib.zb_expert_product(_ptr(hidden), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slots),
                                  max_tiles, ff, width, top, ACTIVATIONS[act], 0, code, _stream()), "expert_product")
     _check(lib.zb_expert_product(_ptr(y), _ptr(hidden), ff, _ptr(w_down), None, _ptr(plan), _ptr(slots), max_tiles,

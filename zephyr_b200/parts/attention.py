@@ -135,9 +135,10 @@ class Attention(Mixer):
         self.group = self.nh // self.nkv
         self.tile_tokens = ops.attention_tile_tokens(self.group)
         self.fused_position = False
-        # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask and sinks
-        # too, for keys and values of one width in bfloat16; everything else stays with the general kernel.
-        equal = self.vd == self.hd and self.softcap == 0.0
+        # The split-context decode kernel and the tensor-core prompt kernel take a chunked mask, sinks and
+        # a bound on the scores too, for keys and values of one width in bfloat16; everything else stays
+        # with the general kernel.
+        equal = self.vd == self.hd
         self.fast_decode = equal and ops.paged_decode_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.fast_prefill = equal and ops.paged_prefill_supported(self.nh, self.nkv, self.hd, self.dtype)
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
@@ -229,7 +230,8 @@ class Attention(Mixer):
         out = torch.empty((q.shape[0], self.nh * self.vd), dtype=q.dtype, device=q.device)
         common = (self.nh, self.nkv, self.hd, self.window, self.scale, ctx.status)
         masks = {"chunk": self.chunk, "sinks": self.sinks} if (self.chunk or self.sinks is not None) else {}
-        general_only = {"softcap": self.softcap} if self.softcap > 0.0 else {}
+        if self.softcap > 0.0:
+            masks["softcap"] = self.softcap
         decode_done = self.fast_decode and ctx.num_decode_rows > 0
         if decode_done:
             ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
@@ -247,8 +249,7 @@ class Attention(Mixer):
         tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
         if tile_row.numel() > 0:
             ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
-                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks,
-                                **general_only)
+                                ctx.row_ctx, *common, out=out, head_slopes=self.score_slopes, value_dim=self.vd, **masks)
         return out
 
     takes_out_dtype = True

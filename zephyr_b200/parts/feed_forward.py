@@ -52,19 +52,18 @@ class SwiGLU(FeedForward):
         }
 
     def as_gated_products(self) -> tuple[torch.Tensor, torch.Tensor] | None:
+        # The chain of small products has SiLU in its epilogue; another activation keeps the layer off it.
         return (self.w_gate_up, self.w_down) if self.blocked and self.activation == "silu" else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.activation != "silu":      # the products with the activation inside are SiLU's
-            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked, act=self.activation)
-            return ops.linear(hidden, self.w_down)
+        act = self.activation
         if self.blocked and x.shape[0] <= ops.SMALL_GEMM_ROWS and ops.gemm_small_supported(x, self.w_gate_up):
-            hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True)       # product and activation in one kernel
+            hidden = ops.gemm_small(x, self.w_gate_up, swiglu=True, act=act)       # product and activation in one kernel
         elif (self.blocked and (x.shape[0] >= ops.GEMM_TC_MIN_ROWS or not ops.USE_LIBRARY_PRODUCTS)
               and ops.gemm_tc_supported(x, self.w_gate_up, swiglu=True)):
-            hidden = ops.gemm_tc(x, self.w_gate_up, swiglu=True)          # the same for a prompt's many rows, on tcgen05
+            hidden = ops.gemm_tc(x, self.w_gate_up, swiglu=True, act=act)          # the same for a prompt's many rows, on tcgen05
         else:
-            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked)
+            hidden = ops.silu_mul(ops.linear(x, self.w_gate_up), blocked=self.blocked, act=act)
         return ops.linear(hidden, self.w_down)
 
 

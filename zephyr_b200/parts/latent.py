@@ -59,6 +59,11 @@ class LatentAttention(Mixer):
         self.w_o = weights[p["o_proj"]]
         self.sinks = weights[p["sinks"]].float().contiguous() if p.get("sinks") else None
         self.tile_tokens = ops.attention_tile_tokens(nh)
+        # In bfloat16 the split-context decode kernel and the tensor-core prompt kernel take the latent
+        # as one key/value head whose keys are its values, where they take its width and head count.
+        self.fast_decode = ops.paged_decode_supported(nh, 1, rank, dtype)
+        self.fast_prefill = ops.paged_prefill_supported(nh, 1, rank, dtype)
+        self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     @staticmethod
     def weight_decls(spec: MixerSpec) -> dict[str, WeightDecl]:
@@ -87,7 +92,8 @@ class LatentAttention(Mixer):
 
     @staticmethod
     def tile_requests(spec: MixerSpec) -> list[tuple[int, str]]:
-        return [(ops.attention_tile_tokens(int(spec.params["num_heads"])), "all")]
+        tokens = ops.attention_tile_tokens(int(spec.params["num_heads"]))
+        return [(tokens, "all"), (tokens, "multi"), (tokens, "single"), (ops.paged_prefill_tile_tokens(), "multi")]
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: LayerCall,
                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -100,15 +106,36 @@ class LatentAttention(Mixer):
             ops.qkv_pairs(projected[:, nh * hd: nh * hd + rank], 0, 1, rank, 0, None, None, self.latent_norm, self.eps,
                           None, 0, ctx.positions, ctx.token_row, cache, table, ctx.status, self.dtype)
         q_latent = ops.head_linear(projected[:, : nh * hd], self.w_q_to_latent)  # [T, nh * rank], the model's type
-        tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, "all")]
-        attended = torch.empty_like(q_latent)
-        if tile_row.numel() > 0:
-            ops.paged_attention(q_latent, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start,
-                                ctx.row_q_len, ctx.row_ctx, nh, 1, rank, 0, self.scale, ctx.status, out=attended,
-                                sinks=self.sinks, shared_kv=True)
+        attended = self.attend(q_latent, ctx, cache, table)
         gate = projected[:, nh * hd + rank:] if self.has_gate else None
         heads_out = ops.head_linear(attended, self.w_latent_to_v, gate=gate)     # [T, nh * vd]
         return ops.linear(heads_out, self.w_o, out_dtype=out_dtype)
+
+    def attend(self, q: torch.Tensor, ctx: StepContext, cache: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        """Attention of the latent-space queries [T, heads * rank] over the cached latents: rows with one
+        new token on the split-context kernel, rows with several on the tensor-core prompt kernel, where
+        those take this shape and type; whatever is left on the general kernel."""
+        out = torch.empty_like(q)
+        common = (self.nh, 1, self.rank, 0, self.scale, ctx.status)
+        decode_done = self.fast_decode and ctx.num_decode_rows > 0
+        if decode_done:
+            ops.paged_decode(q, cache, table, ctx.decode_rows, ctx.row_q_start, ctx.row_ctx, ctx.max_decode_context,
+                             *common, out=out, sinks=self.sinks, keys_only=True)
+        prefill_done = False
+        if self.fast_prefill:
+            tile_row, tile_q0 = ctx.tiles[(self.prefill_tile_tokens, "multi")]
+            prefill_done = True
+            if tile_row.numel() > 0:
+                ops.paged_prefill(q, cache, table, tile_row, tile_q0, ctx.row_q_start, ctx.row_q_len, ctx.row_ctx,
+                                  *common, out=out, sinks=self.sinks, keys_only=True)
+        if decode_done and prefill_done:
+            return out
+        which = "multi" if decode_done else ("single" if prefill_done else "all")
+        tile_row, tile_q0 = ctx.tiles[(self.tile_tokens, which)]
+        if tile_row.numel() > 0:
+            ops.paged_attention(q, cache, table, tile_row, tile_q0, self.tile_tokens, ctx.row_q_start, ctx.row_q_len,
+                                ctx.row_ctx, *common, out=out, sinks=self.sinks, shared_kv=True)
+        return out
 
 
 register_mixer("latent_attention", LatentAttention)
