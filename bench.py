@@ -47,6 +47,16 @@ LEGELIX_SIZES = {
                   gla=dict(heads=16, dim=128, vdim=256), ssm=dict(heads=64, vdim=64, state=128, groups=4)),
 }
 
+# ``--arch gefovik``: the same for the design whose layers norm their parts' outputs: one latent-attention
+# layer in four, the others attention with keys as values, a bound on the scores and a query multiplier;
+# feed-forwards dense (ReLU) and routed (16 experts and 4 identity experts, a token takes 4) in turn.  A
+# routed layer's four experts together are as wide as the dense feed-forward.
+GEFOVIK_SIZES = {
+    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, kv_heads=8, head_dim=128, rank=128, experts=16, identity=4, top=4),
+    "w4096": dict(width=4096, ff=12288, layers=8, heads=32, kv_heads=8, head_dim=128, rank=128, latent_heads=16, experts=16,
+                  identity=4, top=4),
+}
+
 
 def metric_name(args) -> str:
     """One string for both arms: the driver divides their values only if the strings are equal."""
@@ -206,19 +216,41 @@ def build_pair(size: str, batch: int, context: int):
     return legelix, qwen, make
 
 
+def build_gefovik_pair(size: str, batch: int, context: int):
+    """(Gefovik configuration, Qwen3 configuration, engine builder) of one entry of ``GEFOVIK_SIZES``."""
+    from zephyr_b200.config import GefovikConfig
+
+    z = GEFOVIK_SIZES[size]
+    dense = {"kind": "dense", "ff": z["ff"]}
+    routed = {"kind": "moe", "expert": {"ff": z["ff"] // z["top"]},
+              "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"]}}
+    hd = z["head_dim"]
+    latent = {"type": "latent_attention", "mlp": dense,
+              "mixer": dict(heads=z.get("latent_heads", z["heads"]), dim=hd, vdim=hd, kv_rank=z["rank"], scale=hd ** -0.5)}
+    capped = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=30.0,
+                  q_temp={"coef": 0.3, "every": 64})
+    four = [latent, {"type": "attention", "mixer": capped, "mlp": routed}, {"type": "attention", "mixer": capped, "mlp": dense},
+            {"type": "attention", "mixer": capped, "mlp": routed}]
+    gefovik = GefovikConfig(vocab=32768, width=z["width"], layers=tuple(four * (z["layers"] // 4)), norm_eps=1e-6,
+                            embedding_scale=0.5)
+    _, qwen, make = build_pair(size, batch, context)
+    return gefovik, qwen, make
+
+
 def run_legelix(args) -> dict:
     """Prefill of 2048 tokens and a decode step of ``--batch`` requests at ``--context``, device-timed, for
-    every entry of ``LEGELIX_SIZES`` and for the Qwen3 decoder of equal size beside it."""
+    every entry of ``LEGELIX_SIZES`` (or ``GEFOVIK_SIZES``) and for the Qwen3 decoder of equal size beside it."""
     import gc
 
     import torch
 
-    out = {"arch": "legelix", "batch": args.batch, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
+    out = {"arch": args.arch, "batch": args.batch, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "dtype": "bf16",
            "data": "synthetic: seeded random weights and token ids", "sizes": {}}
-    for size in (args.sizes.split(",") if args.sizes else LEGELIX_SIZES):
-        legelix, qwen, make = build_pair(size, args.batch, args.context)
+    table, pair = (LEGELIX_SIZES, build_pair) if args.arch == "legelix" else (GEFOVIK_SIZES, build_gefovik_pair)
+    for size in (args.sizes.split(",") if args.sizes else table):
+        legelix, qwen, make = pair(size, args.batch, args.context)
         row = {}
-        for name, config in (("legelix", legelix), ("qwen3", qwen)):
+        for name, config in ((args.arch, legelix), ("qwen3", qwen)):
             engine = make(config)
             prefill_ms = device_prefill(engine, PREFILL_TOKENS, 3, 5)
             decode_ms, launches, _ = device_decode(engine, args.batch, args.context, args.warmup, args.steps, None)
@@ -516,9 +548,9 @@ def main() -> int:
     parser.add_argument("--no-points", dest="points", action="store_false", help="skip decode at batch 1 and 64")
     parser.add_argument("--own-products", action="store_true",
                         help="with --only: no product on the vendor library (all on this package's tcgen05 kernel)")
-    parser.add_argument("--arch", choices=("qwen3", "legelix"), default="qwen3",
-                        help="legelix: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal size")
-    parser.add_argument("--sizes", default="", help="--arch legelix: entries of LEGELIX_SIZES, with commas (default: all)")
+    parser.add_argument("--arch", choices=("qwen3", "legelix", "gefovik"), default="qwen3",
+                        help="legelix, gefovik: prefill and decode of that design at a few layer sizes, beside Qwen3 of equal size")
+    parser.add_argument("--sizes", default="", help="--arch legelix|gefovik: entries of LEGELIX_SIZES or GEFOVIK_SIZES, with commas (default: all)")
     parser.add_argument("--only", choices=("prefill", "decode"), default=None,
                         help="time only the 2048-token prefill, or only the decode step, and print a short line "
                              "(the program a profiler is pointed at)")
@@ -528,7 +560,7 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.arch == "legelix":
+    if args.arch in ("legelix", "gefovik"):
         print(json.dumps(run_legelix(args)))
         return 0
     if args.only is not None and args.impl == "ours":

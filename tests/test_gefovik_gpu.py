@@ -287,7 +287,8 @@ def _plain_experts(x, ids, weights, gate, up, down):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("tokens,width,ff,experts,identity,top", [(1, 64, 24, 3, 0, 1), (5, 40, 20, 7, 2, 4), (300, 64, 96, 4, 1, 3),
-                                                                 (130, 50, 36, 3, 2, 5), (77, 72, 30, 12, 0, 2)])
+                                                                 (130, 50, 36, 3, 2, 5), (77, 72, 30, 12, 0, 2),
+                                                                 (700, 320, 264, 6, 2, 3), (256, 128, 512, 2, 0, 2)])
 def test_expert_products_and_the_weighted_sum(cuda_device, dtype, tokens, width, ff, experts, identity, top):
     """Given choices: tokens sorted by expert, several tiles for one expert, an expert nobody chose,
     identity experts, widths that take the vector loads and widths that do not."""
@@ -304,12 +305,25 @@ def test_expert_products_and_the_weighted_sum(cuda_device, dtype, tokens, width,
     if experts > 2 and top == 1:
         ids[ids == 1] = 0                                  # expert 1 stays without tokens
     weights = torch.rand(tokens, top, generator=g)
-    got = ops.routed_experts(x.to(cuda_device), ids.to(cuda_device), weights.to(cuda_device), gate.to(cuda_device),
-                             up.to(cuda_device), down.to(cuda_device))
     expected = _plain_experts(x.double(), ids, weights.double(), gate.double(), up.double(), down.double())
-    bound = 2e-5 if dtype == "float32" else 0.03
+    bound = (2e-5 if dtype == "float32" else 0.03) * max(1.0, float(expected.abs().max()))
+    on_device = [t.to(cuda_device) for t in (x, ids, weights)]
+    got = ops.routed_experts(*on_device, gate.to(cuda_device), up.to(cuda_device), down.to(cuda_device))
     assert got.dtype == torch_dtype and torch.isfinite(got).all()
-    assert (got.cpu().double() - expected).abs().max() < bound * max(1.0, float(expected.abs().max()))
+    assert (got.cpu().double() - expected).abs().max() < bound
+    if ff % 8 == 0:
+        # gate and up rows in alternating blocks of 8: the layout the part keeps; with many choices per expert
+        # in bfloat16 both products then run as one grouped launch each on tcgen05, else on the tiles as above
+        both = ops.interleave_gate_up(gate.to(cuda_device), up.to(cuda_device))
+        assert torch.equal(both[:, 8:16], up[:, :8].to(cuda_device)) and torch.equal(both[:, 16:24], gate[:, 8:16].to(cuda_device))
+        for grouped in (True, False):
+            ops.USE_GROUPED_TCGEN05 = grouped
+            try:
+                got = ops.routed_experts(*on_device, both, None, down.to(cuda_device))
+            finally:
+                ops.USE_GROUPED_TCGEN05 = True
+            assert torch.isfinite(got).all() and (got.cpu().double() - expected).abs().max() < bound, grouped
+        ops.check_status(ops.device_status(cuda_device))
 
 
 @pytest.mark.parametrize("x_dtype,w_dtype", [("float32", "float32"), ("bfloat16", "bfloat16"), ("float32", "bfloat16")])

@@ -59,6 +59,9 @@ struct GemmTcArgs {
   int M, N, K;
   int tiles_m, tiles;
   int relu_gate;                 // with the gated epilogue: max(gate, 0) * up instead of silu(gate) * up
+  const int* tile_group;         // null, or per tile of 128 rows the matrix of w (rows group * N .. + N) its rows take;
+                                 // a negative entry: the tile is not computed
+  int groups;                    // matrices stacked in w (1 without tile_group)
   int* status;
 };
 
@@ -198,6 +201,8 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
       unsigned phase = 0;
       for (int tile = blockIdx.x; tile < a.tiles && !sh.failed; tile += gridDim.x) {
         const int m0 = (tile % a.tiles_m) * GT_BM, n0 = (tile / a.tiles_m) * BN;
+        const int group = a.tile_group != nullptr ? a.tile_group[tile % a.tiles_m] : 0;
+        if (group < 0) continue;            // every role skips the same tiles
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!gt_wait(sh, &sh.empty[stage], phase ^ 1)) {
             if (!sh.failed) report(a.status, STATUS_COPY_TIMEOUT, tile, kb);
@@ -207,7 +212,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
           unsigned char* slot = ring + stage * Shape::STAGE_BYTES;
           mbar_arrive_expect_tx(&sh.full[stage], Shape::STAGE_BYTES);
           tiled_copy_2d_g2s(slot, &a.x_map, kb * GT_BK, m0, &sh.full[stage]);
-          tiled_copy_2d_g2s(slot + GT_A_BYTES, &a.w_map, kb * GT_BK, n0, &sh.full[stage]);
+          tiled_copy_2d_g2s(slot + GT_A_BYTES, &a.w_map, kb * GT_BK, group * a.N + n0, &sh.full[stage]);
           if (++stage == Shape::STAGES) {
             stage = 0;
             phase ^= 1;
@@ -221,6 +226,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
       int stage = 0, acc = 0;
       unsigned phase = 0, acc_phase = 0;
       for (int tile = blockIdx.x; tile < a.tiles && !sh.failed; tile += gridDim.x) {
+        if (a.tile_group != nullptr && a.tile_group[tile % a.tiles_m] < 0) continue;
         if (!gt_wait(sh, &sh.acc_empty[acc], acc_phase ^ 1)) {
           if (!sh.failed) report(a.status, STATUS_BARRIER_TIMEOUT, tile, -1);
           sh.failed = 1;
@@ -259,6 +265,7 @@ __global__ void __launch_bounds__(GT_THREADS, 1) gemm_tc_kernel(const __grid_con
     unsigned acc_phase = 0;
     for (int tile = blockIdx.x; tile < a.tiles && !sh.failed; tile += gridDim.x) {
       const int m0 = (tile % a.tiles_m) * GT_BM, n0 = (tile / a.tiles_m) * BN;
+      if (a.tile_group != nullptr && a.tile_group[tile % a.tiles_m] < 0) continue;
       if (!gt_wait(sh, &sh.acc_full[acc], acc_phase)) {
         if (!sh.failed) report(a.status, STATUS_BARRIER_TIMEOUT, tile, -3);
         sh.failed = 1;
@@ -513,7 +520,7 @@ bool matrix_tensor_map(const void* base, long long rows, int cols, long long ld,
 template <int BN, int EPI>
 int gemm_tc_launch(GemmTcArgs& a, const void* w, int sms, cudaStream_t stream) {
   using Shape = GemmTcShape<BN>;
-  if (!matrix_tensor_map(w, a.N, a.K, a.K, BN, &a.w_map)) return ERR_CUDA;
+  if (!matrix_tensor_map(w, static_cast<long long>(a.N) * a.groups, a.K, a.K, BN, &a.w_map)) return ERR_CUDA;
   a.tiles_m = (a.M + GT_BM - 1) / GT_BM;
   a.tiles = a.tiles_m * ((a.N + BN - 1) / BN);
   if (cuda_failed(cudaFuncSetAttribute(gemm_tc_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Shape::SMEM_BYTES)))
@@ -582,6 +589,8 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   GemmTcArgs a;
   a.M = M; a.N = N; a.K = K;
   a.relu_gate = relu_gate;
+  a.tile_group = nullptr;
+  a.groups = 1;
   a.status = status;
   if (!matrix_tensor_map(x, M, K, ldx, GT_BM, &a.x_map)) return ERR_CUDA;
   if (!matrix_tensor_map(y, M, epilogue == GT_EPI_SWIGLU ? N / 2 : N, ldy, 32, &a.y_map, epilogue == GT_EPI_FLOAT ? 4 : 2)) return ERR_CUDA;
@@ -594,4 +603,39 @@ ZB_API int zb_gemm_tc(void* y, const void* x, const void* w, int M, int N, int K
   if (epilogue == GT_EPI_SWIGLU)
     return block_n == 256 ? gemm_tc_launch<256, GT_EPI_SWIGLU>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_SWIGLU>(a, w, sms, s);
   return block_n == 256 ? gemm_tc_launch<256, GT_EPI_PLAIN>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_PLAIN>(a, w, sms, s);
+}
+
+// The same over several matrices stacked in w ([groups * N, K]): x [tiles_m * 128, K] is cut into tiles of
+// 128 rows, and tile i multiplies with matrix tile_group[i] (a device array; a negative entry leaves the
+// tile out, its rows of y unwritten).  Rows sorted by expert and padded to whole tiles make a routed
+// feed-forward's products one launch.  Tiles of one SM; epilogues as zb_gemm_tc.
+ZB_API int zb_gemm_tc_grouped(void* y, const void* x, const void* w, const int* tile_group, int tiles_m, int groups,
+                              int N, int K, long long ldx, int ldy, int epilogue, int* status, void* stream) {
+  if (tiles_m <= 0 || groups <= 0 || tile_group == nullptr) return ERR_BAD_ARGUMENT;
+  const int M = tiles_m * GT_BM;
+  if (!zb_gemm_tc_supported(M, N, K, ldx, ldy, epilogue)) return ERR_UNSUPPORTED;
+  const int relu_gate = epilogue == GT_EPI_RELU_GATE;
+  if (relu_gate) epilogue = GT_EPI_SWIGLU;
+  if (reinterpret_cast<uintptr_t>(y) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(w) % 16 != 0)
+    return ERR_BAD_ARGUMENT;
+  int device = 0, sms = 0;
+  if (cuda_failed(cudaGetDevice(&device)) ||
+      cuda_failed(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)))
+    return ERR_CUDA;
+  GemmTcArgs a;
+  a.M = M; a.N = N; a.K = K;
+  a.relu_gate = relu_gate;
+  a.tile_group = tile_group;
+  a.groups = groups;
+  a.status = status;
+  if (!matrix_tensor_map(x, M, K, ldx, GT_BM, &a.x_map)) return ERR_CUDA;
+  if (!matrix_tensor_map(y, M, epilogue == GT_EPI_SWIGLU ? N / 2 : N, ldy, 32, &a.y_map, epilogue == GT_EPI_FLOAT ? 4 : 2)) return ERR_CUDA;
+  const cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool wide = N >= 256;
+  if (epilogue == GT_EPI_FLOAT)
+    return wide ? gemm_tc_launch<256, GT_EPI_FLOAT>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_FLOAT>(a, w, sms, s);
+  if (epilogue == GT_EPI_SWIGLU)
+    return wide ? gemm_tc_launch<256, GT_EPI_SWIGLU>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_SWIGLU>(a, w, sms, s);
+  return wide ? gemm_tc_launch<256, GT_EPI_PLAIN>(a, w, sms, s) : gemm_tc_launch<128, GT_EPI_PLAIN>(a, w, sms, s);
 }

@@ -140,6 +140,52 @@ align_kernel(int* plan, int* slots, int* place_of_slot, const int* ids, int num_
   }
 }
 
+// The same for products that run as one grouped launch of the tcgen05 kernel (gemm_tc.cu): every expert's
+// run begins on a multiple of `tile_rows` places, tile_group[i] names the expert of tile i (-1: unused),
+// and slots[place] is -1 where a place pads a run.
+__global__ void __launch_bounds__(ALIGN_THREADS)
+align_padded_kernel(int* tile_group, int* slots, int* place_of_slot, const int* ids, int num_slots, int experts,
+                    int max_tiles, int tile_rows) {
+  extern __shared__ int align_smem[];
+  int* count = align_smem;                 // [experts]
+  int* start = count + experts;            // [experts + 1]
+  int* fill = start + experts + 1;         // [experts]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = fill[e] = 0;
+  for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) slots[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < num_slots; i += blockDim.x) {
+    const int e = ids[i];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = tiles * tile_rows;
+      for (int r = 0; r < count[e] && tiles < max_tiles; r += tile_rows) tile_group[tiles++] = e;
+    }
+    for (; tiles < max_tiles; ++tiles) tile_group[tiles] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < num_slots; i += blockDim.x) {
+    const int e = ids[i];
+    int place = -1;
+    if (e >= 0 && e < experts) {
+      place = start[e] + atomicAdd(&fill[e], 1);
+      slots[place] = i;
+    }
+    place_of_slot[i] = place;
+  }
+}
+
+// out[place, :] = x[slots[place] / top, :], zeros where the place pads an expert's run.  16-byte pieces.
+__global__ void gather_places_kernel(uint4* out, const uint4* x, long long x_stride16, const int* slots, int pieces, int top) {
+  const int place = blockIdx.x, slot = slots[place];
+  const uint4* src = slot >= 0 ? x + static_cast<long long>(slot / top) * x_stride16 : nullptr;
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x)
+    out[static_cast<size_t>(place) * pieces + i] = src != nullptr ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
 // ------------------------------------------------------------------------------------------- products
 struct ExpertProductArgs {
   void* out;               // gate/up: hidden [places, ff] in T; down: y [places, width] in float32
@@ -150,7 +196,21 @@ struct ExpertProductArgs {
   const int* slots;
   long long x_stride;
   int N, K, top, act;
+  int interleaved;         // gate/up: w0 is [experts, 2 N, K], blocks of 8 gate rows each followed by its 8 up rows
 };
+
+// Where the tile's first gate row and first up row lie.
+template <typename T>
+__device__ __forceinline__ void gate_up_rows(const ExpertProductArgs& a, int expert, int n0, const T*& gate, const T*& up) {
+  if (a.interleaved) {
+    gate = static_cast<const T*>(a.w0) + (static_cast<size_t>(expert) * 2 * a.N + 2 * n0) * a.K;
+    up = gate + static_cast<size_t>(8) * a.K;
+  } else {
+    const size_t at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+    gate = static_cast<const T*>(a.w0) + at;
+    up = static_cast<const T*>(a.w1) + at;
+  }
+}
 
 __device__ __forceinline__ float expert_act(float g, int act) {
   return act == 1 ? fmaxf(g, 0.0f) : g / (1.0f + expf(-g));
@@ -170,9 +230,10 @@ __global__ void __launch_bounds__(TP_THREADS) expert_gate_up_kernel(const Expert
       src = static_cast<const T*>(a.x) + static_cast<long long>(a.slots[place0 + threadIdx.x] / a.top) * a.x_stride;
     sm.row[threadIdx.x] = src;
   }
-  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  const T *gate, *up;
+  gate_up_rows(a, expert, n0, gate, up);
   float acc[2][2][4];
-  tile_product<T, true>(sm, static_cast<const T*>(a.w0) + w_at, static_cast<const T*>(a.w1) + w_at, a.N - n0, a.K, acc);
+  tile_product<T, true>(sm, gate, up, a.N - n0, a.K, acc, a.interleaved != 0);
   const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
 #pragma unroll
   for (int m = 0; m < 2; ++m) {
@@ -233,10 +294,10 @@ __global__ void __launch_bounds__(TM_THREADS) expert_gate_up_mma_kernel(const Ex
     sm.row[threadIdx.x] = src;
   }
   __syncthreads();
-  const size_t w_at = (static_cast<size_t>(expert) * a.N + n0) * a.K;
+  const T *gate, *up;
+  gate_up_rows(a, expert, n0, gate, up);
   float acc[2][4][4];
-  tile_product_mma<true, T>(sm, static_cast<const T*>(a.w0) + w_at, static_cast<const T*>(a.w1) + w_at, a.N - n0, a.K,
-                            vectors != 0, vectors != 0, acc);
+  tile_product_mma<true, T>(sm, gate, up, a.N - n0, a.K, vectors != 0, vectors != 0, acc, a.interleaved != 0);
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -274,7 +335,7 @@ __global__ void __launch_bounds__(TM_THREADS) expert_down_mma_kernel(const Exper
 
 // -------------------------------------------------------------------------------------------- combine
 template <typename T>
-__global__ void combine_kernel(T* out, const float* y, const T* x, long long x_stride, const int* ids,
+__global__ void combine_kernel(T* out, const float* y, long long y_stride, const T* x, long long x_stride, const int* ids,
                                const float* weights, const int* place_of_slot, int width, int top) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -283,7 +344,7 @@ __global__ void combine_kernel(T* out, const float* y, const T* x, long long x_s
       const int slot = t * top + j, place = place_of_slot[slot];
       const float w = weights[slot];
       // An expert's output takes the model's type before it is weighted, as a layer of its own would leave it.
-      const float v = place >= 0 ? to_float(from_float<T>(y[static_cast<size_t>(place) * width + i]))
+      const float v = place >= 0 ? to_float(from_float<T>(y[static_cast<size_t>(place) * y_stride + i]))
                                  : to_float(x[t * x_stride + i]);
       sum = fmaf(w, v, sum);
     }
@@ -319,14 +380,17 @@ ZB_API int zb_route_align(int* plan, int* slots, int* place_of_slot, const int* 
 }
 
 // `down` = 0: hidden = act(gate x) * (up x), N = ff, K = width; 1: y = down hidden, N = width, K = ff.
+// Without w1 the gate/up product reads w0 as [experts, 2 N, K] in blocks of 8 gate rows and their 8 up rows.
 ZB_API int zb_expert_product(void* out, const void* x, long long x_stride, const void* w0, const void* w1,
                              const int* plan, const int* slots, int max_tiles, int N, int K, int top, int act,
                              int down, int dtype, void* stream) {
   if (max_tiles < 0 || N <= 0 || K <= 0 || top <= 0 || (act != 0 && act != 1)) return ERR_BAD_ARGUMENT;
+  if (!down && w1 == nullptr && N % 8 != 0) return ERR_BAD_ARGUMENT;
   if (max_tiles == 0) return OK;
   ExpertProductArgs a;
   a.out = out; a.x = x; a.w0 = w0; a.w1 = w1; a.plan = plan; a.slots = slots; a.x_stride = x_stride;
   a.N = N; a.K = K; a.top = top; a.act = act;
+  a.interleaved = !down && w1 == nullptr;
   const dim3 grid(max_tiles, (N + TP_BN - 1) / TP_BN);       // both tile forms are 64 outputs wide
   static_assert(TP_BN == TM_BN, "one grid for both forms");
   auto s = static_cast<cudaStream_t>(stream);
@@ -343,7 +407,29 @@ ZB_API int zb_expert_product(void* out, const void* x, long long x_stride, const
   return launch_result();
 }
 
-ZB_API int zb_route_combine(void* out, const float* y, const void* x, long long x_stride, const int* ids,
+ZB_API int zb_route_align_padded(int* tile_group, int* slots, int* place_of_slot, const int* ids, int num_slots,
+                                 int experts, int max_tiles, int tile_rows, void* stream) {
+  if (num_slots < 0 || experts <= 0 || max_tiles <= 0 || tile_rows <= 0) return ERR_BAD_ARGUMENT;
+  const size_t smem = (3 * static_cast<size_t>(experts) + 1) * sizeof(int);
+  if (smem > 48 * 1024) return ERR_UNSUPPORTED;
+  align_padded_kernel<<<1, ALIGN_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(tile_group, slots, place_of_slot, ids,
+                                                                                       num_slots, experts, max_tiles, tile_rows);
+  return launch_result();
+}
+
+// out [places, width] = the tokens' rows in the order of `slots` (bfloat16; width a multiple of 8, 16-byte aligned rows).
+ZB_API int zb_gather_places(void* out, const void* x, long long x_stride, const int* slots, int places, int width,
+                            int top, void* stream) {
+  if (places < 0 || width <= 0 || width % 8 != 0 || x_stride % 8 != 0 || top <= 0 ||
+      reinterpret_cast<uintptr_t>(out) % 16 != 0 || reinterpret_cast<uintptr_t>(x) % 16 != 0)
+    return ERR_BAD_ARGUMENT;
+  if (places == 0) return OK;
+  gather_places_kernel<<<places, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(out), static_cast<const uint4*>(x), x_stride / 8, slots, width / 8, top);
+  return launch_result();
+}
+
+ZB_API int zb_route_combine(void* out, const float* y, long long y_stride, const void* x, long long x_stride, const int* ids,
                             const float* weights, const int* place_of_slot, int tokens, int width, int top, int dtype,
                             void* stream) {
   if (tokens < 0 || width <= 0 || top <= 0) return ERR_BAD_ARGUMENT;
@@ -351,10 +437,10 @@ ZB_API int zb_route_combine(void* out, const float* y, const void* x, long long 
   auto s = static_cast<cudaStream_t>(stream);
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == DTYPE_F32)
-    combine_kernel<float><<<tokens, threads, 0, s>>>(static_cast<float*>(out), y, static_cast<const float*>(x), x_stride,
+    combine_kernel<float><<<tokens, threads, 0, s>>>(static_cast<float*>(out), y, y_stride, static_cast<const float*>(x), x_stride,
                                                      ids, weights, place_of_slot, width, top);
   else
-    combine_kernel<__nv_bfloat16><<<tokens, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), y,
+    combine_kernel<__nv_bfloat16><<<tokens, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), y, y_stride,
                                                              static_cast<const __nv_bfloat16*>(x), x_stride, ids, weights,
                                                              place_of_slot, width, top);
   return launch_result();

@@ -28,7 +28,7 @@ struct TileProductSmem {
 // The rows of A are of type TA (they may be float32 beside bfloat16 weights), the weights of type T.
 template <typename T, bool DUAL, typename TA = T>
 __device__ __forceinline__ void tile_product(TileProductSmem& sm, const T* w0, const T* w1, int n_left, int K,
-                                             float (&acc)[2][2][4]) {
+                                             float (&acc)[2][2][4], bool interleaved = false) {
   const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
 #pragma unroll
   for (int m = 0; m < 2; ++m)
@@ -46,8 +46,10 @@ __device__ __forceinline__ void tile_product(TileProductSmem& sm, const T* w0, c
     for (int e = tid; e < TP_BN * TP_BK; e += TP_THREADS) {
       const int n = e / TP_BK, c = e - n * TP_BK;
       const bool ok = n < n_left && k0 + c < K;
-      sm.b[0][n][c] = ok ? to_float(w0[static_cast<size_t>(n) * K + k0 + c]) : 0.0f;
-      if (DUAL) sm.b[1][n][c] = ok ? to_float(w1[static_cast<size_t>(n) * K + k0 + c]) : 0.0f;
+      // `interleaved`: the matrices' rows alternate in blocks of 8 (row n of each lies 16 (n / 8) + n % 8 rows in).
+      const size_t row = interleaved ? static_cast<size_t>((n >> 3) * 16 + (n & 7)) : static_cast<size_t>(n);
+      sm.b[0][n][c] = ok ? to_float(w0[row * K + k0 + c]) : 0.0f;
+      if (DUAL) sm.b[1][n][c] = ok ? to_float(w1[row * K + k0 + c]) : 0.0f;
     }
     __syncthreads();
 #pragma unroll 8

@@ -48,7 +48,7 @@ __device__ __forceinline__ uint4 tm_row_piece(const TA* row, int k, int K, bool 
 template <bool DUAL, typename TA>
 __device__ __forceinline__ void tile_product_mma(TileMmaSmem& sm, const __nv_bfloat16* w0, const __nv_bfloat16* w1,
                                                  int n_left, int K, bool a_vectors, bool w_vectors,
-                                                 float (&acc)[2][4][4]) {
+                                                 float (&acc)[2][4][4], bool interleaved = false) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3, m0 = (warp & 3) * 16, n0 = (warp >> 2) * 32;
 #pragma unroll
@@ -58,17 +58,29 @@ __device__ __forceinline__ void tile_product_mma(TileMmaSmem& sm, const __nv_bfl
 #pragma unroll
       for (int c = 0; c < 4; ++c) acc[s][nt][c] = 0.0f;
   const int r = tid >> 2, piece = (tid & 3) * 8;         // this thread stages 8 columns of row r (A) and of output r (W)
+  const TA* a_row = static_cast<const TA*>(sm.row[r]);
+  const bool real = r < n_left;
+  // `interleaved`: the matrices' rows alternate in blocks of 8 (row r of each lies 16 (r / 8) + r % 8 rows in).
+  const size_t w_row = interleaved ? static_cast<size_t>((r >> 3) * 16 + (r & 7)) : static_cast<size_t>(r);
+  const __nv_bfloat16* w0_row = real ? w0 + w_row * K : nullptr;
+  const __nv_bfloat16* w1_row = DUAL && real ? w1 + w_row * K : nullptr;
+  // The pieces of the step after this one are asked for before this step's products, so that their
+  // way from memory runs beside the tensor cores' work.
+  uint4 av = tm_row_piece(a_row, piece, K, a_vectors);
+  uint4 bv0 = tm_row_piece(w0_row, piece, K, w_vectors);
+  uint4 bv1 = make_uint4(0, 0, 0, 0);
+  if (DUAL) bv1 = tm_row_piece(w1_row, piece, K, w_vectors);
   for (int k0 = 0; k0 < K; k0 += TM_BK) {
-    const uint4 av = tm_row_piece(static_cast<const TA*>(sm.row[r]), k0 + piece, K, a_vectors);
-    const bool real = r < n_left;
-    const uint4 bv0 = tm_row_piece(real ? w0 + static_cast<size_t>(r) * K : nullptr, k0 + piece, K, w_vectors);
-    uint4 bv1 = make_uint4(0, 0, 0, 0);
-    if (DUAL) bv1 = tm_row_piece(real ? w1 + static_cast<size_t>(r) * K : nullptr, k0 + piece, K, w_vectors);
     __syncthreads();                                      // the step before is no longer read
     *reinterpret_cast<uint4*>(&sm.a[r][piece]) = av;
     *reinterpret_cast<uint4*>(&sm.b[0][r][piece]) = bv0;
     if (DUAL) *reinterpret_cast<uint4*>(&sm.b[1][r][piece]) = bv1;
     __syncthreads();
+    if (k0 + TM_BK < K) {
+      av = tm_row_piece(a_row, k0 + TM_BK + piece, K, a_vectors);
+      bv0 = tm_row_piece(w0_row, k0 + TM_BK + piece, K, w_vectors);
+      if (DUAL) bv1 = tm_row_piece(w1_row, k0 + TM_BK + piece, K, w_vectors);
+    }
 #pragma unroll
     for (int kk = 0; kk < TM_BK; kk += 16) {
       unsigned a[4];

@@ -63,8 +63,12 @@ _SIGNATURES = {
     "zb_route_align": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_expert_product": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_int, c_void_p],
-    "zb_route_combine": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                         c_int, c_void_p],
+    "zb_route_align_padded": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "zb_gather_places": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
+    "zb_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int,
+                           c_void_p, c_void_p],
+    "zb_route_combine": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                         c_int, c_int, c_void_p],
     "zb_add_bias": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -1270,43 +1274,87 @@ def route(logits: torch.Tensor, correction: torch.Tensor | None, top: int) -> tu
     return ids, weights
 
 
-def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                   w_down: torch.Tensor, act: str = "silu") -> torch.Tensor:
+GROUPED_TILE_ROWS = 128        # rows of a tile of the tcgen05 product
+GROUPED_MIN_ROWS_PER_EXPERT = 0    # the grouped tcgen05 products from this many choices per expert on (on average)
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[E, ff, width] twice -> [E, 2 ff, width] in blocks of 8 gate rows each followed by its 8 up rows
+    (ff a multiple of 8): the layout whose product can apply act(gate) * up where the sums leave the tensor
+    cores."""
+    E, ff, width = w_gate.shape
+    return torch.stack([w_gate.view(E, ff // 8, 8, width), w_up.view(E, ff // 8, 8, width)], dim=2).reshape(E, 2 * ff, width).contiguous()
+
+
+def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate: torch.Tensor,
+                   w_up: torch.Tensor | None, w_down: torch.Tensor, act: str = "silu") -> torch.Tensor:
     """sum_j weights[t, j] * expert_{ids[t, j]}(x[t]) for x [T, width]: expert e < E is
     w_down[e] (act(w_gate[e] x) * (w_up[e] x)) with w_gate, w_up [E, ff, width] and w_down [E, width, ff]; an
-    id >= E names an identity expert, whose output is x itself.  Three launches over the tokens sorted
-    by expert (gate/up with the activation, down, the weighted sum); nothing comes back to the host."""
+    id >= E names an identity expert, whose output is x itself.  Without ``w_up``, ``w_gate`` holds both
+    matrices as ``interleave_gate_up`` lays them out.  The tokens are sorted by expert on the device and
+    nothing comes back to the host: alignment, the two products (gate/up with the activation, down) and the
+    weighted sum.  bfloat16 with many tokens per expert and the interleaved layout: each product is ONE
+    grouped launch of the tcgen05 kernel over runs padded to whole tiles; otherwise tiles on mma.sync
+    (bfloat16) or CUDA cores (float32)."""
     _cuda(x, ids, weights, w_gate, w_up, w_down)
     T, width = x.shape
     top = ids.shape[1]
-    E, ff, _ = w_gate.shape
-    _require(x.stride(1) == 1 and x.dtype in DTYPE_CODE and all(w.dtype == x.dtype and w.is_contiguous()
+    interleaved = w_up is None
+    E = w_gate.shape[0]
+    ff = w_gate.shape[1] // 2 if interleaved else w_gate.shape[1]
+    _require(x.stride(1) == 1 and x.dtype in DTYPE_CODE and all(w is None or (w.dtype == x.dtype and w.is_contiguous())
              for w in (w_gate, w_up, w_down)), "tokens and expert matrices of one type")
-    _require(w_gate.shape == (E, ff, width) and w_up.shape == (E, ff, width) and w_down.shape == (E, width, ff),
-             "expert matrices [E, ff, width], [E, ff, width], [E, width, ff]")
+    _require(w_gate.shape == ((E, 2 * ff, width) if interleaved else (E, ff, width)) and (interleaved or w_up.shape == (E, ff, width))
+             and w_down.shape == (E, width, ff) and (not interleaved or ff % 8 == 0),
+             "expert matrices [E, ff, width] (or [E, 2 ff, width] interleaved), [E, width, ff]")
     _require(act in ACTIVATIONS, f"the gate's activation is one of {sorted(ACTIVATIONS)}")
     _i32(ids)
     _require(weights.dtype == torch.float32 and weights.is_contiguous() and weights.shape == ids.shape, "one weight per choice")
     lib, device = library(), x.device
     num_slots = T * top
     code = DTYPE_CODE[x.dtype]
-    tile_rows = lib.zb_expert_tile_rows(code)          # CUDA-core tiles in float32, tensor-core tiles in bfloat16
-    max_tiles = -(-num_slots // tile_rows) + E
-    plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=device)
-    slots = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
-    place = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
-    _check(lib.zb_route_align(_ptr(plan), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, max_tiles, tile_rows,
-                              _stream()), "route_align")
-    hidden = torch.empty((max(num_slots, 1), ff), dtype=x.dtype, device=device)
-    y = torch.empty((max(num_slots, 1), width), dtype=torch.float32, device=device)
-    _check(lib.zb_expert_product(_ptr(hidden), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slots),
-                                 max_tiles, ff, width, top, ACTIVATIONS[act], 0, code, _stream()), "expert_product")
-    _check(lib.zb_expert_product(_ptr(y), _ptr(hidden), ff, _ptr(w_down), None, _ptr(plan), _ptr(slots), max_tiles,
-                                 width, ff, top, ACTIVATIONS[act], 1, code, _stream()), "expert_product")
     out = torch.empty((T, width), dtype=x.dtype, device=device)
-    _check(lib.zb_route_combine(_ptr(out), _ptr(y), _ptr(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(place), T,
+    place = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
+    grouped = (USE_GROUPED_TCGEN05 and interleaved and x.dtype == torch.bfloat16 and width % 8 == 0 and x.stride(0) % 8 == 0
+               and num_slots >= GROUPED_MIN_ROWS_PER_EXPERT * E)
+    if grouped:
+        tiles = -(-num_slots // GROUPED_TILE_ROWS) + E
+        places = tiles * GROUPED_TILE_ROWS
+        tile_group = torch.empty(tiles, dtype=torch.int32, device=device)
+        slots = torch.empty(places, dtype=torch.int32, device=device)
+        _check(lib.zb_route_align_padded(_ptr(tile_group), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, tiles,
+                                         GROUPED_TILE_ROWS, _stream()), "route_align")
+        rows = torch.empty((places, width), dtype=x.dtype, device=device)
+        _check(lib.zb_gather_places(_ptr(rows), _ptr(x), x.stride(0), _ptr(slots), places, width, top, _stream()),
+               "gather_places")
+        status = device_status(device)
+        hidden = torch.empty((places, ff), dtype=x.dtype, device=device)
+        _check(lib.zb_gemm_tc_grouped(_ptr(hidden), _ptr(rows), _ptr(w_gate), _ptr(tile_group), tiles, E, 2 * ff, width, width,
+                                      ff, 3 if act == "relu" else 1, _ptr(status), _stream()), "gemm_tc_grouped")
+        ldy = (width + 3) // 4 * 4
+        y = torch.empty((places, ldy), dtype=torch.float32, device=device)
+        _check(lib.zb_gemm_tc_grouped(_ptr(y), _ptr(hidden), _ptr(w_down), _ptr(tile_group), tiles, E, width, ff, ff, ldy, 2,
+                                      _ptr(status), _stream()), "gemm_tc_grouped")
+    else:
+        tile_rows = lib.zb_expert_tile_rows(code)          # CUDA-core tiles in float32, tensor-core tiles in bfloat16
+        max_tiles = -(-num_slots // tile_rows) + E
+        plan = torch.empty(1 + 3 * max_tiles, dtype=torch.int32, device=device)
+        slots = torch.empty(max(num_slots, 1), dtype=torch.int32, device=device)
+        _check(lib.zb_route_align(_ptr(plan), _ptr(slots), _ptr(place), _ptr(ids), num_slots, E, max_tiles, tile_rows,
+                                  _stream()), "route_align")
+        hidden = torch.empty((max(num_slots, 1), ff), dtype=x.dtype, device=device)
+        ldy = width
+        y = torch.empty((max(num_slots, 1), width), dtype=torch.float32, device=device)
+        _check(lib.zb_expert_product(_ptr(hidden), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(plan), _ptr(slots),
+                                     max_tiles, ff, width, top, ACTIVATIONS[act], 0, code, _stream()), "expert_product")
+        _check(lib.zb_expert_product(_ptr(y), _ptr(hidden), ff, _ptr(w_down), None, _ptr(plan), _ptr(slots), max_tiles,
+                                     width, ff, top, ACTIVATIONS[act], 1, code, _stream()), "expert_product")
+    _check(lib.zb_route_combine(_ptr(out), _ptr(y), ldy, _ptr(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(place), T,
                                 width, top, code, _stream()), "route_combine")
     return out
+
+
+USE_GROUPED_TCGEN05 = True      # off: a routed layer's products stay on the mma.sync tiles whatever the token count
 
 
 # ------------------------------------------------------------------------------ sampling

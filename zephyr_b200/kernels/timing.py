@@ -11,6 +11,9 @@
     python -m zephyr_b200.kernels.timing conv_silu --n 2560 [--tokens 0 --rows 8]
     python -m zephyr_b200.kernels.timing norms --hidden 2048 --n 2048
     python -m zephyr_b200.kernels.timing decode_attention --context 1024 --chunk 1024
+    python -m zephyr_b200.kernels.timing decode_attention --softcap 30 | --keys-only --kv-heads 1
+    python -m zephyr_b200.kernels.timing experts --tokens 2048 --hidden 2048 --ffn 1536 --experts 16 --top 4
+    python -m zephyr_b200.kernels.timing head_linear --tokens 2048 --heads 16 --n 128 --k 128
 
 Each case rotates over several copies of its large operands, together larger than the L2 cache, so
 that a kernel bound by memory is timed against memory and not against L2.  Time is taken with CUDA
@@ -67,12 +70,12 @@ def _copies(bytes_each: int) -> int:
 SEQUENTIAL_PAGES = False      # --sequential-pages: a request's pages lie behind one another in the pool
 
 
-def _paged_inputs(batch: int, context: int, nkv: int, hd: int, page: int, device):
+def _paged_inputs(batch: int, context: int, nkv: int, hd: int, page: int, device, keys_only: bool = False):
     pages_per = math.ceil(context / page)
     num_pages = batch * pages_per + 1
-    cache_bytes = num_pages * 2 * nkv * page * hd * 2
-    caches = [torch.randn((num_pages, 2, nkv, page, hd), device=device, dtype=torch.bfloat16)
-              for _ in range(_copies(cache_bytes))]
+    shape = (num_pages, nkv * page * hd) if keys_only else (num_pages, 2, nkv, page, hd)
+    cache_bytes = num_pages * (1 if keys_only else 2) * nkv * page * hd * 2
+    caches = [torch.randn(shape, device=device, dtype=torch.bfloat16) for _ in range(_copies(cache_bytes))]
     order = torch.arange(num_pages - 1, device=device) if SEQUENTIAL_PAGES else torch.randperm(num_pages - 1, device=device)
     table = (order[: batch * pages_per] + 1).int().view(batch, pages_per)
     return caches, table.contiguous()
@@ -81,7 +84,7 @@ def _paged_inputs(batch: int, context: int, nkv: int, hd: int, page: int, device
 def decode_attention(args) -> dict:
     device = torch.device("cuda")
     nh, nkv, hd, B, ctx = args.heads, args.kv_heads, args.head_dim, args.batch, args.context
-    caches, table = _paged_inputs(B, ctx, nkv, hd, args.page_size, device)
+    caches, table = _paged_inputs(B, ctx, nkv, hd, args.page_size, device, args.keys_only)
     q = torch.randn((B, nh * hd), device=device, dtype=torch.bfloat16)
     rows = torch.arange(B, dtype=torch.int32, device=device)
     row_ctx = torch.full((B,), ctx - 1, dtype=torch.int32, device=device)
@@ -89,6 +92,7 @@ def decode_attention(args) -> dict:
     split = args.split or None
     chunk = getattr(args, "chunk", 0)
     masks = dict(chunk=chunk, sinks=torch.zeros(nh, device=device)) if chunk else {}
+    masks.update(softcap=args.softcap, keys_only=args.keys_only)
 
     def run(i):
         ops.paged_decode(q, caches[i % len(caches)], table, rows, rows, row_ctx, ctx, nh, nkv, hd, args.window,
@@ -103,8 +107,8 @@ def decode_attention(args) -> dict:
     live = min(ctx, args.window) if args.window else ctx
     if chunk:
         live = min(live, (ctx - 1) % chunk + 1)
-    read = B * live * nkv * hd * 2 * 2
-    return {"kernel": "paged_decode_kernel", "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+    read = B * live * nkv * hd * 2 * (1 if args.keys_only else 2)
+    return {"kernel": "paged_decode_kernel", "softcap": args.softcap, "keys_only": args.keys_only, "batch": B, "context": ctx, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "page_size": args.page_size, "window": args.window, "chunk": chunk, "split_size": split or "balanced", "us": round(us, 2),
             "bytes_read": read, "gbs": round(read / us / 1e3, 1), "timeline_ns": _decode_timeline(trace)}
 
@@ -131,7 +135,7 @@ def _decode_timeline(trace: torch.Tensor) -> dict:
 def prefill_attention(args) -> dict:
     device = torch.device("cuda")
     nh, nkv, hd, T = args.heads, args.kv_heads, args.head_dim, args.tokens
-    caches, table = _paged_inputs(1, T, nkv, hd, args.page_size, device)
+    caches, table = _paged_inputs(1, T, nkv, hd, args.page_size, device, args.keys_only)
     q = torch.randn((T, nh * hd), device=device, dtype=torch.bfloat16)
     tile = ops.paged_prefill_tile_tokens()
     n_tiles = math.ceil(T / tile)
@@ -142,6 +146,7 @@ def prefill_attention(args) -> dict:
     status, out = ops.new_status(device), torch.empty_like(q)
     chunk = getattr(args, "chunk", 0)
     masks = dict(chunk=chunk, sinks=torch.zeros(nh, device=device)) if chunk else {}
+    masks.update(softcap=args.softcap, keys_only=args.keys_only)
 
     def run(i):
         ops.paged_prefill(q, caches[i % len(caches)], table, tile_row, tile_q0, zero, q_len, zero, nh, nkv, hd,
@@ -156,7 +161,7 @@ def prefill_attention(args) -> dict:
     # Two products of 2 * hd flops per (query, visible key) pair and head.
     pairs = sum(min(t + 1, args.window) if args.window else (t % chunk + 1 if chunk else t + 1) for t in range(T))
     flops = 4 * hd * pairs * nh
-    return {"kernel": "paged_prefill_kernel", "chunk": chunk, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
+    return {"kernel": "paged_prefill_kernel", "chunk": chunk, "softcap": args.softcap, "keys_only": args.keys_only, "tokens": T, "heads": nh, "kv_heads": nkv, "head_dim": hd,
             "page_size": args.page_size, "window": args.window, "us": round(us, 2), "flops": flops,
             "tflops": round(flops / us / 1e6, 1), "longest_cta_ns": _prefill_timeline(trace)}
 
@@ -434,6 +439,46 @@ def norms(args) -> dict:
 CASES.update({"state_scan": state_scan, "conv_silu": conv_silu, "norms": norms})
 
 
+def experts(args) -> dict:
+    """A routed feed-forward's products: ``--tokens`` tokens of width ``--hidden``, each taking ``--top`` of
+    ``--experts`` experts of inner size ``--ffn`` (uniform random choices), routing excluded.  With few
+    tokens the bound is the bytes of the experts that were hit, with many the products."""
+    device, bf = torch.device("cuda"), torch.bfloat16
+    T, H, F, E, top = args.tokens, args.hidden, args.ffn, args.experts, args.top
+    copies = _copies(3 * E * F * H * 2)
+    # gate and up rows in alternating blocks of 8, as the routed part keeps them
+    gate_up = [torch.randn((E, 2 * F, H), device=device, dtype=bf) * H ** -0.5 for _ in range(copies)]
+    down = [torch.randn((E, H, F), device=device, dtype=bf) * F ** -0.5 for _ in range(copies)]
+    x = torch.randn((T, H), device=device, dtype=bf)
+    ids = torch.stack([torch.randperm(E, device=device)[:top] for _ in range(T)]).int().contiguous()
+    weights = torch.rand((T, top), device=device)
+    ops.USE_GROUPED_TCGEN05 = not args.legacy_prefill        # --legacy-prefill: the mma.sync tiles whatever the token count
+    us = _time(lambda i: ops.routed_experts(x, ids, weights, gate_up[i % copies], None, down[i % copies]),
+               args.warmup, args.iters)
+    hit = int(torch.unique(ids).numel())
+    flops = 2.0 * T * top * 3 * F * H
+    read = hit * 3 * F * H * 2
+    ops.check_status(ops.device_status(device), "experts")
+    return {"kernel": "route_align + expert products + combine", "tokens": T, "hidden": H, "ffn": F, "experts": E, "top": top,
+            "experts_hit": hit, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "weights_gbs": round(read / us / 1e3, 1)}
+
+
+def head_linear(args) -> dict:
+    """The product per head: ``--tokens`` rows of ``--heads`` heads, [n, k] per head."""
+    device, bf = torch.device("cuda"), torch.bfloat16
+    T, heads, N, K = args.tokens, args.heads, args.n, args.k
+    copies = _copies(T * heads * (N + K) * 2)
+    x = [torch.randn((T, heads * K), device=device, dtype=bf) for _ in range(copies)]
+    w = torch.randn((heads, N, K), device=device, dtype=bf)
+    us = _time(lambda i: ops.head_linear(x[i % copies], w), args.warmup, args.iters)
+    flops, moved = 2.0 * T * heads * N * K, T * heads * (N + K) * 2 + heads * N * K * 2
+    return {"kernel": "head_linear_mma_kernel", "tokens": T, "heads": heads, "n": N, "k": K, "us": round(us, 2),
+            "tflops": round(flops / us / 1e6, 1), "gbs": round(moved / us / 1e3, 1)}
+
+
+CASES.update({"experts": experts, "head_linear": head_linear})
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="python -m zephyr_b200.kernels.timing", description=__doc__.split("\n")[0])
     parser.add_argument("case", choices=sorted(CASES))
@@ -448,6 +493,10 @@ def main(argv=None) -> int:
     parser.add_argument("--page-size", type=int, default=16)
     parser.add_argument("--window", type=int, default=0)
     parser.add_argument("--chunk", type=int, default=0, help="attention: a chunked mask of this size, with sinks")
+    parser.add_argument("--softcap", type=float, default=0.0, help="attention: scores bounded by softcap * tanh(s / softcap)")
+    parser.add_argument("--keys-only", action="store_true", help="attention: a cache of keys that are the values too")
+    parser.add_argument("--experts", type=int, default=16)
+    parser.add_argument("--top", type=int, default=4)
     parser.add_argument("--value-dim", type=int, default=128, help="state_scan: value channels per head")
     parser.add_argument("--mode", choices=("gated", "state_space"), default="gated")
     parser.add_argument("--segment", type=int, default=-1, help="state_scan: tokens of a segment (0: one piece; -1: chosen)")

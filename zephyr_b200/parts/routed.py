@@ -43,10 +43,16 @@ class RoutedFeedForward(FeedForward):
             raise ConfigError(f"an expert's activation is one of {sorted(ops.ACTIVATIONS)}")
         self.w_router = weights[p["router"]]
         self.correction = weights[p["correction"]].float().contiguous() if p.get("correction") else None
+        if outputs > ops.route_max_outputs():
+            raise ConfigError(f"the routing kernel takes up to {ops.route_max_outputs()} router outputs, not {outputs}")
         names = p["expert_names"]
         self.w_gate = torch.stack([weights[gate] for gate, _, _ in names]).contiguous()
         self.w_up = torch.stack([weights[up] for _, up, _ in names]).contiguous()
         self.w_down = torch.stack([weights[down] for _, _, down in names]).contiguous()
+        if self.intermediate % 8 == 0:
+            # Blocks of 8 gate rows and their 8 up rows: the layout whose product applies the activation
+            # where the sums leave the tensor cores.  The separate matrices are not kept beside it.
+            self.w_gate, self.w_up = ops.interleave_gate_up(self.w_gate, self.w_up), None
 
     @staticmethod
     def weight_decls(spec: FeedForwardSpec) -> dict[str, WeightDecl]:
@@ -65,7 +71,7 @@ class RoutedFeedForward(FeedForward):
         return decls
 
     def weights_read(self) -> list[torch.Tensor]:
-        return [self.w_router, self.w_gate, self.w_up, self.w_down]
+        return [w for w in (self.w_router, self.w_gate, self.w_up, self.w_down) if w is not None]
 
     def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
