@@ -356,7 +356,8 @@ def _rows(n, at, device):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("dim,heads,kv_heads,softcap,temp,page", [(32, 4, 2, 3.0, (0.5, 7), 16), (64, 8, 1, 0.0, None, 32),
                                                                  (16, 2, 2, 1.0, (2.0, 64), 16), (96, 6, 2, 8.0, (0.25, 1), 16),
-                                                                 (128, 2, 1, 0.0, (1.0, 16), 16), (24, 3, 3, 5.0, None, 16)])
+                                                                 (128, 2, 1, 0.0, (1.0, 16), 16), (24, 3, 3, 5.0, None, 16),
+                                                                 (15, 3, 1, 2.0, (0.5, 9), 16), (320, 2, 2, 6.0, None, 16)])
 def test_capped_attention_with_keys_as_values(cuda_device, dtype, dim, heads, kv_heads, softcap, temp, page):
     """Queries of head 0 point at one key each: a key hundreds of positions back, the first key of the
     sequence, the key just before.  Unit-RMS queries and keys, the multiplier by position, the bound on
@@ -432,7 +433,8 @@ def test_capped_attention_with_keys_as_values(cuda_device, dtype, dim, heads, kv
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("rank,heads,page", [(48, 3, 16), (64, 4, 16), (96, 6, 32), (128, 16, 16), (20, 2, 16), (32, 20, 16)])
+@pytest.mark.parametrize("rank,heads,page", [(48, 3, 16), (64, 4, 16), (96, 6, 32), (128, 16, 16), (20, 2, 16), (32, 20, 16),
+                                             (37, 2, 16), (300, 3, 16), (512, 2, 32)])
 def test_attention_over_keys_that_are_the_values(cuda_device, dtype, rank, heads, page):
     """One key/value head whose cache keeps keys only (the latent of latent attention), every query head
     reading it, with a sink per head: queries that point at a latent far back, at the first one and at

@@ -1,5 +1,5 @@
 // Paged causal attention on CUDA cores, float32 arithmetic throughout: the kernel of the true
-// 32-bit path, and the general one (any head size in steps of 16 up to 256, any head and group
+// 32-bit path, and the general one (any head size up to 512, any head and group
 // counts, any page size, with or without a window, any mixture of prompt portions and single
 // decoded tokens).
 //
@@ -168,10 +168,11 @@ paged_attention_simt_kernel(const AttentionArgs a) {
       float s = 0.0f;
       const float* qp = q_s + p * kd;
       const T* kr = k_s + lane * kstride;
-      for (int d = 0; d < kd; d += 2) {
+      for (int d = 0; d + 1 < kd; d += 2) {
         s = fmaf(qp[d], to_float(kr[d]), s);
         s = fmaf(qp[d + 1], to_float(kr[d + 1]), s);
       }
+      if (kd & 1) s = fmaf(qp[kd - 1], to_float(kr[kd - 1]), s);
       s *= a.scale;
       if (a.softcap > 0.0f) s = a.softcap * tanhf(s / a.softcap);
       s = valid ? fmaf(slope, static_cast<float>(kp - qpos), s) : -INFINITY;
@@ -240,6 +241,9 @@ int attention_simt_dispatch(const AttentionArgs& a, int n_tiles, int head_chunks
     case 6: return attention_simt_launch<T, 6>(a, n_tiles, head_chunks, stream);
     case 7: return attention_simt_launch<T, 7>(a, n_tiles, head_chunks, stream);
     case 8: return attention_simt_launch<T, 8>(a, n_tiles, head_chunks, stream);
+    case 9: case 10: return attention_simt_launch<T, 10>(a, n_tiles, head_chunks, stream);
+    case 11: case 12: return attention_simt_launch<T, 12>(a, n_tiles, head_chunks, stream);
+    case 13: case 14: case 15: case 16: return attention_simt_launch<T, 16>(a, n_tiles, head_chunks, stream);
     default: return ERR_UNSUPPORTED;
   }
 }
@@ -267,7 +271,7 @@ ZB_API int zb_paged_attention_simt(void* out, const void* q, const void* kv_cach
   if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || kd <= 0 || vd <= 0 || page_size <= 0 || n_tiles < 0 || window < 0 ||
       chunk < 0 || softcap < 0.0f || (shared_kv && kd != vd))
     return ERR_BAD_ARGUMENT;
-  if (kd % 2 != 0 || kd > 256 || vd > 256) return ERR_UNSUPPORTED;
+  if (kd > 512 || vd > 512) return ERR_UNSUPPORTED;
   if (n_tiles == 0) return OK;
   const int g = nh / nkv;
   const int heads_per_chunk = g < ATT_MAX_PAIRS ? g : ATT_MAX_PAIRS;

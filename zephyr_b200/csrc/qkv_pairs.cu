@@ -22,7 +22,7 @@
 namespace zb {
 
 constexpr int QP_WARPS = 4;
-constexpr int QP_PAIRS = 4;        // pairs per lane: widths up to 256
+constexpr int QP_PAIRS = 8;        // pairs per lane: widths up to 512
 
 struct QkvPairsArgs {
   void* q_out;               // [T, nh * kd]

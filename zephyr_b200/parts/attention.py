@@ -63,12 +63,12 @@ class Attention(Mixer):
         self.dtype = dtype
         if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv != 0:
             raise ConfigError("attention needs positive head counts with heads divisible by kv_heads")
-        if self.hd <= 0 or self.hd > 256:
-            raise ConfigError(f"attention kernels take head sizes up to 256, not {self.hd}")
+        if self.hd <= 0 or self.hd > 512:
+            raise ConfigError(f"attention kernels take head sizes up to 512, not {self.hd}")
         self.vd = int(p.get("value_dim") or self.hd)
         self.chunk = int(p.get("chunk") or 0)
-        if self.vd <= 0 or self.vd > 256 or self.chunk < 0:
-            raise ConfigError("attention takes value widths up to 256 and a chunk size that is not negative")
+        if self.vd <= 0 or self.vd > 512 or self.chunk < 0:
+            raise ConfigError("attention takes value widths up to 512 and a chunk size that is not negative")
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
         if self.values_from_keys and self.vd != self.hd:
             raise ConfigError("values that are the keys have the keys' width")
@@ -123,8 +123,8 @@ class Attention(Mixer):
         self.prefill_tile_tokens = ops.paged_prefill_tile_tokens()
 
     def _init_general(self, p) -> None:
-        if self.hd % 2 != 0:
-            raise ConfigError("the general attention path takes even key widths")
+        if self.hd % 2 != 0 and self.pair_freqs is not None:
+            raise ConfigError("a rotation of adjacent pairs takes even key widths")
         if self.score_slopes_wanted():
             raise ConfigError("a bias on the scores and the general path's extras do not combine")
         if self.position is not None and self.pair_freqs is None and self.position.as_rotation_tables() != (None, None):

@@ -44,8 +44,8 @@ class LatentAttention(Mixer):
         self.dtype = dtype
         if min(self.nh, self.hd, self.vd, self.rank) <= 0:
             raise ConfigError("latent attention needs positive head count, head sizes and rank")
-        if self.rank % 2 != 0 or self.rank > 256:
-            raise ConfigError(f"latent attention takes an even latent size of at most 256, not {self.rank}")
+        if self.rank > 512:
+            raise ConfigError(f"latent attention takes a latent size of at most 512, not {self.rank}")
         nh, hd, vd, rank = self.nh, self.hd, self.vd, self.rank
         gate = weights[p["gate"]] if p.get("gate") else None
         # One product for everything that reads the layer's input: queries, the latent, the gates.
