@@ -22,7 +22,7 @@
 namespace zb {
 
 constexpr int QP_WARPS = 4;
-constexpr int QP_PAIRS = 8;        // pairs per lane: widths up to 512
+constexpr int QP_MAX_PAIRS = 8;    // pairs per lane: widths up to 512; a launch takes 1, 2, 4 or 8 by its widest head
 
 struct QkvPairsArgs {
   void* q_out;               // [T, nh * kd]
@@ -64,7 +64,7 @@ __device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
-template <typename IN, typename T>
+template <typename IN, typename T, int QP_PAIRS>
 __global__ void __launch_bounds__(QP_WARPS * 32) qkv_pairs_kernel(const QkvPairsArgs a) {
   const int t = blockIdx.x, lane = threadIdx.x & 31;
   const int head = blockIdx.y * QP_WARPS + (threadIdx.x >> 5);
@@ -201,7 +201,7 @@ ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const fl
       (q_temp_coef != 0.0f && q_temp_every <= 0) ||
       (unit_norm && (q_norm_w != nullptr || k_norm_w != nullptr)))
     return ERR_BAD_ARGUMENT;
-  if (kd > 64 * QP_PAIRS || vd > 64 * QP_PAIRS) return ERR_UNSUPPORTED;
+  if (kd > 64 * QP_MAX_PAIRS || vd > 64 * QP_MAX_PAIRS) return ERR_UNSUPPORTED;
   if (tokens == 0) return OK;
   QkvPairsArgs a;
   a.q_out = q_out; a.qkv = qkv; a.stride = stride; a.bias = bias; a.q_norm_w = q_norm_w; a.k_norm_w = k_norm_w;
@@ -217,13 +217,18 @@ ZB_API int zb_qkv_pairs(void* q_out, const void* qkv, long long stride, const fl
   const int heads = cache != nullptr ? nh + (vd > 0 ? 2 : 1) * nkv : nh;
   const dim3 grid(tokens, (heads + QP_WARPS - 1) / QP_WARPS);
   auto s = static_cast<cudaStream_t>(stream);
-  if (dtype == DTYPE_F32) {
-    if (in_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
-    qkv_pairs_kernel<float, float><<<grid, QP_WARPS * 32, 0, s>>>(a);
-  } else if (in_dtype == DTYPE_F32) {
-    qkv_pairs_kernel<float, __nv_bfloat16><<<grid, QP_WARPS * 32, 0, s>>>(a);
-  } else {
-    qkv_pairs_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, QP_WARPS * 32, 0, s>>>(a);
+  if (dtype == DTYPE_F32 && in_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
+  const int widest = kd > vd ? kd : vd;
+#define ZB_QP(PAIRS)                                                                                         \
+  {                                                                                                          \
+    if (dtype == DTYPE_F32) qkv_pairs_kernel<float, float, PAIRS><<<grid, QP_WARPS * 32, 0, s>>>(a);          \
+    else if (in_dtype == DTYPE_F32) qkv_pairs_kernel<float, __nv_bfloat16, PAIRS><<<grid, QP_WARPS * 32, 0, s>>>(a); \
+    else qkv_pairs_kernel<__nv_bfloat16, __nv_bfloat16, PAIRS><<<grid, QP_WARPS * 32, 0, s>>>(a);             \
   }
+  if (widest <= 64) ZB_QP(1)
+  else if (widest <= 128) ZB_QP(2)
+  else if (widest <= 256) ZB_QP(4)
+  else ZB_QP(8)
+#undef ZB_QP
   return launch_result();
 }

@@ -404,6 +404,10 @@ def norms(args) -> dict:
     us = _time(lambda i: ops.residual_layer_norm(residual32[i % n], delta[i % n], w[0], w[1], 1e-6, 0.5, w[2], w[3], 1e-6),
                args.warmup, args.iters)
     out["residual_layer_norm"] = {"us": round(us, 2), "gbs": round(T * H * 12 / us / 1e3, 1)}
+    # the form of a block that norms its parts' outputs only: one norm without a shift, and the sum rounded for the next part
+    us = _time(lambda i: ops.residual_layer_norm(residual32[i % n], delta[i % n], w[0], None, 1e-6, 1.0, rounded_sum=True),
+               args.warmup, args.iters)
+    out["residual_layer_norm_rounded_sum"] = {"us": round(us, 2), "gbs": round(T * H * 12 / us / 1e3, 1)}
     us = _time(lambda i: ops.add_rmsnorm(residual16[i % n], delta[i % n], w[0], 1e-6), args.warmup, args.iters)
     out["add_rmsnorm"] = {"us": round(us, 2), "gbs": round(T * H * 8 / us / 1e3, 1)}
     W = args.n
@@ -427,6 +431,13 @@ def norms(args) -> dict:
     us = _time(lambda i: ops.qkv_pairs(qkv32[i % len(qkv32)], nh, nkv, hd, hd, bias, ones, ones, 1e-6, freqs, hd, positions,
                                        token_row, cache, table, status, bf), args.warmup, args.iters)
     out["qkv_pairs"] = {"width": width, "us": round(us, 2), "gbs": round(T * width * 6 / us / 1e3, 1)}
+    # the same kernel for keys that are the values: unit norms without scales, a multiplier by position, no value columns
+    narrow = (nh + nkv) * hd
+    us = _time(lambda i: ops.qkv_pairs(qkv32[i % len(qkv32)][:, :narrow], nh, nkv, hd, hd, None, None, None, 1e-6, None, 0,
+                                       positions, token_row, cache, table, status, bf, unit_norm=True, values_from_keys=True,
+                                       q_temp=(0.3, 64)), args.warmup, args.iters)
+    moved = T * (narrow * 4 + (nh + 2 * nkv) * hd * 2)
+    out["qkv_pairs_keys_as_values"] = {"width": narrow, "us": round(us, 2), "gbs": round(moved / us / 1e3, 1)}
     cos, sin = torch.ones((T, hd // 2), device=device), torch.zeros((T, hd // 2), device=device)
     ones16 = ones.to(bf)
     us = _time(lambda i: ops.qk_norm_rope_cache(qkv16[i % len(qkv16)], nh, nkv, hd, ones16, ones16, 1e-6, cos, sin, positions,
