@@ -72,6 +72,10 @@ struct PrefillTcArgs {
   int max_blocks, page_shift, num_pages, num_rows;
   int nh, nkv, window;
   float scale_log2;
+  float softcap_log2;            // > 0: scores are softcap * tanh(scale * s / softcap); this is softcap * log2(e)
+  float scale_over_cap;          // scale / softcap
+  int keys_only;                 // a page holds keys alone, [nkv][page_size][hd], and they are the values too
+  const float* sinks;            // null, or [nh]: exp(sinks[h]) joins the softmax's denominator of head h
   int* status;
   int* trace;                    // null, or 4 ints per tile of the first CTA (the longest work of the launch): the global
                                  // timer (ns, low 32 bits) when S of the tile was issued, when its softmax began (S
@@ -97,12 +101,22 @@ __device__ __forceinline__ float exp2_approx(float x) {
   return y;
 }
 
+// tanh from the special-function unit's exp2 and reciprocal, 1 - 2 / (e^(2x) + 1): absolute error about 1e-7 over
+// the whole line (the unit's own tanh is good to 2^-11 only, which would move a score capped at 30 by 0.02).
+__device__ __forceinline__ float tanh_from_exp2(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(exp2_approx(x * 2.8853900817779268f) + 1.0f));
+  return fmaf(-2.0f, r, 1.0f);
+}
+
 // One half (64 columns) of a row of S (this thread's TMEM lane) -> probabilities exp2(s * scale + neg_shift)
 // as 32 words of two bfloat16 each, their sum, and the largest raw score.  MASKED: column i counts only if
 // after < i <= last and i >= first (positions relative to the tile's first key).
-template <bool MASKED>
+// CAPPED: the exponent is cap_log2 * tanh(raw * scale) + neg_shift, `scale` then being scale / softcap.
+template <bool MASKED, bool CAPPED>
 __device__ __forceinline__ void softmax_pass(unsigned tmem_row, unsigned (&words)[TC_BN / 4], int half, float scale, float neg_shift,
-                                             int last, int first, int after, float& raw_max, float& row_sum) {
+                                             int last, int first, int after, float& raw_max, float& row_sum,
+                                             float cap_log2 = 0.0f) {
   // Four running maxima and sums side by side: with one warp per scheduler a single chain of 128
   // dependent additions would cost its full latency 128 times.
   float max4[4] = {raw_max, -INFINITY, -INFINITY, -INFINITY}, sum4[4] = {row_sum, 0.0f, 0.0f, 0.0f};
@@ -121,7 +135,8 @@ __device__ __forceinline__ void softmax_pass(unsigned tmem_row, unsigned (&words
         const int column = c4 * 32 + i + e;
         const bool ok = !MASKED || (column <= last && column >= first && column > after);
         if (ok) max4[(i >> 1) & 3] = fmaxf(max4[(i >> 1) & 3], raw);
-        p[e] = ok ? exp2_approx(fmaf(raw, scale, neg_shift)) : 0.0f;
+        const float exponent = CAPPED ? fmaf(cap_log2, tanh_from_exp2(raw * scale), neg_shift) : fmaf(raw, scale, neg_shift);
+        p[e] = ok ? exp2_approx(exponent) : 0.0f;
         sum4[(i >> 1) & 3] += p[e];
       }
       words[16 * cc + (i >> 1)] = pack_bf16(p[0], p[1]);
@@ -246,7 +261,8 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
     const int kv = lk / TC_KIND_THREADS, lt = lk % TC_KIND_THREADS; // 0: keys, 1: values; 0..63 within the kind
     const int chunk = lt & 15, row_in_4 = lt >> 4;                // 16-byte copies: this thread's chunk of rows row_in_4 + 4 i
     const int* table = a.block_table + static_cast<size_t>(row) * a.max_blocks;
-    const long long v_offset = static_cast<long long>(a.nkv) * page_size * TC_HD;
+    const int planes = a.keys_only ? 1 : 2;                       // a page's halves: keys and values, or keys that are both
+    const long long v_offset = a.keys_only ? 0LL : static_cast<long long>(a.nkv) * page_size * TC_HD;
     const unsigned dst_base = (chunk >> 3) * TC_HALF_BYTES + ((chunk & 7) << 4);
     // A tile that lies wholly inside [lo, hi) comes by TMA: one tiled copy per page and 64-dim half
     // (the map's box is a page's rows by 64 dims, copied as they lie: the cache's own chunk
@@ -291,7 +307,7 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
           report(a.status, STATUS_PAGE_OUT_OF_RANGE, pg, tok0);
           pg = 0;                       // the bytes must arrive all the same
         }
-        const int cache_row = ((pg * 2 + kv) * a.nkv + kvh) * page_size + (pos & (page_size - 1));
+        const int cache_row = ((pg * planes + (a.keys_only ? 0 : kv)) * a.nkv + kvh) * page_size + (pos & (page_size - 1));
         tiled_copy_2d_g2s(dst + half * TC_HALF_BYTES + piece * rows_per_copy * 128, &a.cache_map, half * 64, cache_row, bar);
       }
       if (j + 1 < n_tiles) {
@@ -323,7 +339,7 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
               report(a.status, STATUS_PAGE_OUT_OF_RANGE, page[i], tok0);
               ok = false;
             } else {
-              src += ((static_cast<long long>(page[i]) * 2 * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD +
+              src += ((static_cast<long long>(page[i]) * planes * a.nkv + kvh) * page_size + (pos & (page_size - 1))) * TC_HD +
                      chunk * 8 + (kv ? v_offset : 0);
             }
           }
@@ -413,6 +429,7 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
     const unsigned tmem_o = tmem_base + lane_base + 2 * TC_BN;
     const int qp = ctx + q0 + r;
     float m_used = -INFINITY, l_run = 0.0f;
+    const bool capped = a.softcap_log2 > 0.0f;
     bool failed = false;
     for (int j = 0; j < n_tiles; ++j) {
       const int k0 = first_tile + j * TC_BN;
@@ -436,11 +453,18 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
       for (int attempt = 0; attempt < 2; ++attempt) {
         const float neg_shift = m_used == -INFINITY ? 0.0f : -m_used;
         float raw_max = -INFINITY, row_sum = 0.0f;
-        if (open_tile)
-          softmax_pass<false>(tmem_s, words, half, a.scale_log2, neg_shift, 0, 0, 0, raw_max, row_sum);
-        else
-          softmax_pass<true>(tmem_s, words, half, a.scale_log2, neg_shift, qp - k0, lo - k0,
-                             a.window > 0 ? qp - a.window - k0 : -(1 << 30), raw_max, row_sum);
+        const int after = a.window > 0 ? qp - a.window - k0 : -(1 << 30);
+        if (capped) {
+          if (open_tile)
+            softmax_pass<false, true>(tmem_s, words, half, a.scale_over_cap, neg_shift, 0, 0, 0, raw_max, row_sum, a.softcap_log2);
+          else
+            softmax_pass<true, true>(tmem_s, words, half, a.scale_over_cap, neg_shift, qp - k0, lo - k0, after, raw_max, row_sum,
+                                     a.softcap_log2);
+        } else if (open_tile) {
+          softmax_pass<false, false>(tmem_s, words, half, a.scale_log2, neg_shift, 0, 0, 0, raw_max, row_sum);
+        } else {
+          softmax_pass<true, false>(tmem_s, words, half, a.scale_log2, neg_shift, qp - k0, lo - k0, after, raw_max, row_sum);
+        }
         if (attempt == 0) {
           // The row's largest score is the larger of its halves'.
           half_note[j & 1][half][r] = raw_max;
@@ -448,7 +472,8 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
           if (!__all_sync(0xffffffffu, wait(&halves_met[j & 1], (j >> 1) & 1))) { give_up(-8); failed = true; break; }
           raw_max = fmaxf(raw_max, half_note[j & 1][half ^ 1][r]);
         }
-        const float row_max = raw_max * a.scale_log2;       // the scale is positive
+        // The scale is positive and the bound grows with its argument: the largest raw score gives the largest exponent.
+        const float row_max = capped ? a.softcap_log2 * tanh_from_exp2(raw_max * a.scale_over_cap) : raw_max * a.scale_log2;
         const bool grow = attempt == 0 && (row_max > m_used + TC_RESCALE_THRESHOLD || (m_used == -INFINITY && row_max > -INFINITY));
         if (!__any_sync(0xffffffffu, grow)) {
           l_run += row_sum;
@@ -494,7 +519,9 @@ paged_prefill_tc_kernel(const __grid_constant__ PrefillTcArgs a) {
     }
     if (!failed) {
       tc_fence_after_sync();
-      const float l_row = half_note[n_tiles & 1][0][r] + half_note[n_tiles & 1][1][r];
+      float l_row = half_note[n_tiles & 1][0][r] + half_note[n_tiles & 1][1][r];
+      // The sink: one more exponential, relative to the shift the row's sums were formed with (both in powers of two).
+      if (a.sinks != nullptr && m_used > -INFINITY) l_row += exp2f(a.sinks[head] * 1.4426950408889634f - m_used);
       const float inv = l_row > 0.0f ? 1.0f / l_row : 0.0f;
       // The keys' and values' stages are free by now (every product is complete): each warp puts its 32
       // rows x 64 columns there, 16-byte pieces permuted by the row so that neither the writes (a
@@ -593,12 +620,15 @@ ZB_API int zb_paged_prefill_tc_supported(int nh, int nkv, int hd, int dtype, int
 }
 
 // Attention of the tiles' tokens (tiles of 128 new tokens of one request) over their requests'
-// pages; writes those tokens' rows of `out`.  Arguments as zb_paged_prefill.
-ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
-                               int page_size, int num_pages, int num_rows, const int* tile_row, const int* tile_q0,
-                               int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
-                               int nkv, int hd, int window, float scale, int* status, void* stream) {
-  if (n_tiles < 0 || page_size <= 0 || window < 0) return ERR_BAD_ARGUMENT;
+// pages; writes those tokens' rows of `out`.  Arguments as zb_paged_prefill_masked without the chunked mask:
+// `softcap` > 0 bounds the scaled scores by softcap * tanh(. / softcap); `keys_only`: a page holds keys alone
+// and they are the values too; `sinks` (null, or one float32 per query head) join the softmax's denominator.
+ZB_API int zb_paged_prefill_tc_masked(void* out, const void* q, const void* kv_cache, const int* block_table,
+                                      int max_blocks, int page_size, int num_pages, int num_rows, const int* tile_row,
+                                      const int* tile_q0, int n_tiles, const int* row_q_start, const int* row_q_len,
+                                      const int* row_ctx, int nh, int nkv, int hd, int window, float scale, float softcap,
+                                      int keys_only, const float* sinks, int* status, void* stream) {
+  if (n_tiles < 0 || page_size <= 0 || window < 0 || softcap < 0.0f) return ERR_BAD_ARGUMENT;
   if (!zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_BF16, page_size)) return ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(q) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0 ||
       reinterpret_cast<uintptr_t>(kv_cache) % 16 != 0)
@@ -606,7 +636,7 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
   if (n_tiles == 0) return OK;
   if (n_tiles > 65535) return ERR_UNSUPPORTED;
   PrefillTcArgs a;
-  const long long cache_rows = static_cast<long long>(num_pages) * 2 * nkv * page_size;
+  const long long cache_rows = static_cast<long long>(num_pages) * (keys_only ? 1 : 2) * nkv * page_size;
   a.tiled = cache_rows < (1LL << 31) &&
             cache_tensor_map(static_cast<const __nv_bfloat16*>(kv_cache), cache_rows, hd, page_size < TC_BN ? page_size : TC_BN,
                              &a.cache_map) ? 1 : 0;
@@ -620,6 +650,10 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
   while ((1 << a.page_shift) < page_size) ++a.page_shift;
   a.nh = nh; a.nkv = nkv; a.window = window;
   a.scale_log2 = scale * 1.4426950408889634f;
+  a.softcap_log2 = softcap * 1.4426950408889634f;
+  a.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
+  a.keys_only = keys_only;
+  a.sinks = sinks;
   a.status = status;
   a.trace = prefill_tc_trace();
   const size_t smem = 2 * TC_STAGES * TC_TILE_BYTES;
@@ -627,4 +661,13 @@ ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, c
     return ERR_CUDA;
   paged_prefill_tc_kernel<<<dim3(nh, n_tiles), TC_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
   return launch_result();
+}
+
+ZB_API int zb_paged_prefill_tc(void* out, const void* q, const void* kv_cache, const int* block_table, int max_blocks,
+                               int page_size, int num_pages, int num_rows, const int* tile_row, const int* tile_q0,
+                               int n_tiles, const int* row_q_start, const int* row_q_len, const int* row_ctx, int nh,
+                               int nkv, int hd, int window, float scale, int* status, void* stream) {
+  return zb_paged_prefill_tc_masked(out, q, kv_cache, block_table, max_blocks, page_size, num_pages, num_rows, tile_row,
+                                    tile_q0, n_tiles, row_q_start, row_q_len, row_ctx, nh, nkv, hd, window, scale, 0.0f, 0,
+                                    nullptr, status, stream);
 }

@@ -119,6 +119,9 @@ _SIGNATURES = {
                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_paged_prefill_tc_supported": [c_int, c_int, c_int, c_int, c_int],
     "zb_paged_prefill_tc_set_trace": [c_void_p],
+    "zb_paged_prefill_tc_masked": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                                   c_void_p, c_void_p, c_void_p],
     "zb_paged_prefill_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "zb_gemm_small_supported": [c_int, c_int, c_int],
@@ -967,31 +970,28 @@ def paged_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Te
                   keys_only: bool = False) -> torch.Tensor:
     """Tensor-core attention for rows with several new tokens, cut into tiles of
     ``paged_prefill_tile_tokens()``; writes those tokens' rows of ``out``.  ``chunk``, ``sinks`` and
-    ``softcap`` as in ``paged_attention``, ``keys_only`` as its ``shared_kv``; with any of them the mma.sync
-    kernel runs, at every head size."""
+    ``softcap`` as in ``paged_attention``, ``keys_only`` as its ``shared_kv``.  Head size 128 runs on tcgen05
+    with the accumulators in tensor memory (every form but the chunked mask), other sizes and chunked masks
+    on mma.sync."""
     _cuda(q, kv_cache, block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx, status, out)
     _i32(block_table, tile_row, tile_q0, row_q_start, row_q_len, row_ctx)
     _require(q.dim() == 2 and q.is_contiguous() and q.shape[1] == nh * hd and q.dtype == torch.bfloat16, "q shape")
     _require(out.shape == q.shape and out.dtype == q.dtype and out.is_contiguous(), "out must match q")
     pages, page_size = _cache_geometry(kv_cache, nkv, hd, 0, q.dtype) if keys_only else _check_cache(kv_cache, nkv, hd, q.dtype)
-    if chunk or sinks is not None or softcap or keys_only:
-        _cuda(sinks)
-        _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
-                 "one float32 sink per query head")
-        _check(library().zb_paged_prefill_masked(
-            _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
-            block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
-            _ptr(row_ctx), nh, nkv, hd, int(window), int(chunk), float(scale), float(softcap), int(keys_only),
-            _ptr(sinks), _ptr(status), _stream()), "paged_prefill")
-        return out
-    # Head size 128 runs on tcgen05 with the accumulators in tensor memory; other sizes on mma.sync.
-    tensor_memory = USE_TCGEN05_PREFILL and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype],
-                                                                                     page_size))
-    kernel = library().zb_paged_prefill_tc if tensor_memory else library().zb_paged_prefill
-    _check(kernel(
-        _ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
-        block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
-        _ptr(row_ctx), nh, nkv, hd, int(window), float(scale), _ptr(status), _stream()), "paged_prefill")
+    _cuda(sinks)
+    _require(sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == nh),
+             "one float32 sink per query head")
+    tensor_memory = (USE_TCGEN05_PREFILL and not chunk
+                     and bool(library().zb_paged_prefill_tc_supported(nh, nkv, hd, DTYPE_CODE[q.dtype], page_size)))
+    common = (_ptr(out), _ptr(q), _ptr(kv_cache), _ptr(block_table), block_table.shape[1], page_size, pages,
+              block_table.shape[0], _ptr(tile_row), _ptr(tile_q0), tile_row.numel(), _ptr(row_q_start), _ptr(row_q_len),
+              _ptr(row_ctx), nh, nkv, hd, int(window))
+    if tensor_memory:
+        _check(library().zb_paged_prefill_tc_masked(*common, float(scale), float(softcap), int(keys_only), _ptr(sinks),
+                                                    _ptr(status), _stream()), "paged_prefill")
+    else:
+        _check(library().zb_paged_prefill_masked(*common, int(chunk), float(scale), float(softcap), int(keys_only),
+                                                 _ptr(sinks), _ptr(status), _stream()), "paged_prefill")
     return out
 
 
