@@ -334,8 +334,9 @@ __global__ void __launch_bounds__(TM_THREADS) expert_down_mma_kernel(const Exper
 }
 
 // -------------------------------------------------------------------------------------------- combine
-template <typename T>
-__global__ void combine_kernel(T* out, const float* y, long long y_stride, const T* x, long long x_stride, const int* ids,
+// Y: the type the experts' outputs come in, float32 sums (rounded to T here) or T itself.
+template <typename T, typename Y>
+__global__ void combine_kernel(T* out, const Y* y, long long y_stride, const T* x, long long x_stride, const int* ids,
                                const float* weights, const int* place_of_slot, int width, int top) {
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -344,7 +345,7 @@ __global__ void combine_kernel(T* out, const float* y, long long y_stride, const
       const int slot = t * top + j, place = place_of_slot[slot];
       const float w = weights[slot];
       // An expert's output takes the model's type before it is weighted, as a layer of its own would leave it.
-      const float v = place >= 0 ? to_float(from_float<T>(y[static_cast<size_t>(place) * y_stride + i]))
+      const float v = place >= 0 ? to_float(from_float<T>(to_float(y[static_cast<size_t>(place) * y_stride + i])))
                                  : to_float(x[t * x_stride + i]);
       sum = fmaf(w, v, sum);
     }
@@ -429,19 +430,28 @@ ZB_API int zb_gather_places(void* out, const void* x, long long x_stride, const 
   return launch_result();
 }
 
-ZB_API int zb_route_combine(void* out, const float* y, long long y_stride, const void* x, long long x_stride, const int* ids,
-                            const float* weights, const int* place_of_slot, int tokens, int width, int top, int dtype,
-                            void* stream) {
+// `y_dtype`: float32 sums, or the model's type (what the grouped tcgen05 product writes).
+ZB_API int zb_route_combine(void* out, const void* y, long long y_stride, int y_dtype, const void* x, long long x_stride,
+                            const int* ids, const float* weights, const int* place_of_slot, int tokens, int width, int top,
+                            int dtype, void* stream) {
   if (tokens < 0 || width <= 0 || top <= 0) return ERR_BAD_ARGUMENT;
   if (tokens == 0) return OK;
   auto s = static_cast<cudaStream_t>(stream);
   const int threads = width >= 1024 ? 256 : 128;
-  if (dtype == DTYPE_F32)
-    combine_kernel<float><<<tokens, threads, 0, s>>>(static_cast<float*>(out), y, y_stride, static_cast<const float*>(x), x_stride,
-                                                     ids, weights, place_of_slot, width, top);
-  else
-    combine_kernel<__nv_bfloat16><<<tokens, threads, 0, s>>>(static_cast<__nv_bfloat16*>(out), y, y_stride,
-                                                             static_cast<const __nv_bfloat16*>(x), x_stride, ids, weights,
-                                                             place_of_slot, width, top);
+  using bf16 = __nv_bfloat16;
+  if (dtype == DTYPE_F32) {
+    if (y_dtype != DTYPE_F32) return ERR_BAD_ARGUMENT;
+    combine_kernel<float, float><<<tokens, threads, 0, s>>>(static_cast<float*>(out), static_cast<const float*>(y), y_stride,
+                                                            static_cast<const float*>(x), x_stride, ids, weights,
+                                                            place_of_slot, width, top);
+  } else if (y_dtype == DTYPE_F32) {
+    combine_kernel<bf16, float><<<tokens, threads, 0, s>>>(static_cast<bf16*>(out), static_cast<const float*>(y), y_stride,
+                                                           static_cast<const bf16*>(x), x_stride, ids, weights, place_of_slot,
+                                                           width, top);
+  } else {
+    combine_kernel<bf16, bf16><<<tokens, threads, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(y), y_stride,
+                                                          static_cast<const bf16*>(x), x_stride, ids, weights, place_of_slot,
+                                                          width, top);
+  }
   return launch_result();
 }

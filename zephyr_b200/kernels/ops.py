@@ -67,8 +67,8 @@ _SIGNATURES = {
     "zb_gather_places": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p],
     "zb_gemm_tc_grouped": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_int, c_int,
                            c_void_p, c_void_p],
-    "zb_route_combine": [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                         c_int, c_int, c_void_p],
+    "zb_route_combine": [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                         c_int, c_int, c_int, c_void_p],
     "zb_add_bias": [c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "zb_qk_norm_rope_cache": [c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p,
                               c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -1331,9 +1331,10 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
         hidden = torch.empty((places, ff), dtype=x.dtype, device=device)
         _check(lib.zb_gemm_tc_grouped(_ptr(hidden), _ptr(rows), _ptr(w_gate), _ptr(tile_group), tiles, E, 2 * ff, width, width,
                                       ff, 3 if act == "relu" else 1, _ptr(status), _stream()), "gemm_tc_grouped")
-        ldy = (width + 3) // 4 * 4
-        y = torch.empty((places, ldy), dtype=torch.float32, device=device)
-        _check(lib.zb_gemm_tc_grouped(_ptr(y), _ptr(hidden), _ptr(w_down), _ptr(tile_group), tiles, E, width, ff, ff, ldy, 2,
+        # An expert's output takes the model's type before it is weighted on every path: here the product writes it so.
+        ldy = width
+        y = torch.empty((places, ldy), dtype=x.dtype, device=device)
+        _check(lib.zb_gemm_tc_grouped(_ptr(y), _ptr(hidden), _ptr(w_down), _ptr(tile_group), tiles, E, width, ff, ff, ldy, 0,
                                       _ptr(status), _stream()), "gemm_tc_grouped")
     else:
         tile_rows = lib.zb_expert_tile_rows(code)          # CUDA-core tiles in float32, tensor-core tiles in bfloat16
@@ -1349,8 +1350,8 @@ def routed_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_
                                      max_tiles, ff, width, top, ACTIVATIONS[act], 0, code, _stream()), "expert_product")
         _check(lib.zb_expert_product(_ptr(y), _ptr(hidden), ff, _ptr(w_down), None, _ptr(plan), _ptr(slots), max_tiles,
                                      width, ff, top, ACTIVATIONS[act], 1, code, _stream()), "expert_product")
-    _check(lib.zb_route_combine(_ptr(out), _ptr(y), ldy, _ptr(x), x.stride(0), _ptr(ids), _ptr(weights), _ptr(place), T,
-                                width, top, code, _stream()), "route_combine")
+    _check(lib.zb_route_combine(_ptr(out), _ptr(y), ldy, DTYPE_CODE[y.dtype], _ptr(x), x.stride(0), _ptr(ids), _ptr(weights),
+                                _ptr(place), T, width, top, code, _stream()), "route_combine")
     return out
 
 
