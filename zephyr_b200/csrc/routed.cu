@@ -353,6 +353,41 @@ __global__ void combine_kernel(T* out, const Y* y, long long y_stride, const T* 
   }
 }
 
+// The same for bfloat16 rows of a multiple of 8 elements on 16-byte boundaries: a thread owns 8 neighbouring
+// elements and moves them as one piece; the choices' places are read once per token.
+constexpr int COMBINE_MAX_TOP = 16;
+__global__ void combine_pieces_kernel(uint4* out, const uint4* y, long long y_stride16, const uint4* x, long long x_stride16,
+                                      const float* weights, const int* place_of_slot, int pieces, int top) {
+  const int t = blockIdx.x;
+  __shared__ int place_s[COMBINE_MAX_TOP];
+  __shared__ float weight_s[COMBINE_MAX_TOP];
+  if (threadIdx.x < top) {
+    place_s[threadIdx.x] = place_of_slot[t * top + threadIdx.x];
+    weight_s[threadIdx.x] = weights[t * top + threadIdx.x];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
+    float sum[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) sum[u] = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      const int place = place_s[j];
+      const uint4 v = place >= 0 ? y[static_cast<long long>(place) * y_stride16 + i] : x[t * x_stride16 + i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float2 f = __bfloat1622float2(h[u]);
+        sum[2 * u] = fmaf(weight_s[j], f.x, sum[2 * u]);
+        sum[2 * u + 1] = fmaf(weight_s[j], f.y, sum[2 * u + 1]);
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(sum[0], sum[1]); o.y = pack_bf16(sum[2], sum[3]);
+    o.z = pack_bf16(sum[4], sum[5]); o.w = pack_bf16(sum[6], sum[7]);
+    out[static_cast<size_t>(t) * pieces + i] = o;
+  }
+}
+
 }  // namespace zb
 
 using namespace zb;
@@ -448,6 +483,11 @@ ZB_API int zb_route_combine(void* out, const void* y, long long y_stride, int y_
     combine_kernel<bf16, float><<<tokens, threads, 0, s>>>(static_cast<bf16*>(out), static_cast<const float*>(y), y_stride,
                                                            static_cast<const bf16*>(x), x_stride, ids, weights, place_of_slot,
                                                            width, top);
+  } else if (width % 8 == 0 && y_stride % 8 == 0 && x_stride % 8 == 0 && top <= COMBINE_MAX_TOP && tm_aligned(out, 16) &&
+             tm_aligned(y, 16) && tm_aligned(x, 16)) {
+    combine_pieces_kernel<<<tokens, width >= 2048 ? 256 : 128, 0, s>>>(
+        static_cast<uint4*>(out), static_cast<const uint4*>(y), y_stride / 8, static_cast<const uint4*>(x), x_stride / 8,
+        weights, place_of_slot, width / 8, top);
   } else {
     combine_kernel<bf16, bf16><<<tokens, threads, 0, s>>>(static_cast<bf16*>(out), static_cast<const bf16*>(y), y_stride,
                                                           static_cast<const bf16*>(x), x_stride, ids, weights, place_of_slot,
