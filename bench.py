@@ -49,12 +49,12 @@ LEGELIX_SIZES = {
 
 # ``--arch gefovik``: the same for the design whose layers norm their parts' outputs: one latent-attention
 # layer in four, the others attention with keys as values, a bound on the scores and a query multiplier;
-# feed-forwards dense (ReLU) and routed (16 experts and 4 identity experts, a token takes 4) in turn.  A
+# feed-forwards dense (ReLU) and routed (16 experts and 2 identity experts, a token takes 4) in turn.  A
 # routed layer's four experts together are as wide as the dense feed-forward.
 GEFOVIK_SIZES = {
-    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, kv_heads=8, head_dim=128, rank=128, experts=16, identity=4, top=4),
+    "w2048": dict(width=2048, ff=6144, layers=8, heads=16, kv_heads=8, head_dim=128, rank=128, experts=16, identity=2, top=4),
     "w4096": dict(width=4096, ff=12288, layers=8, heads=32, kv_heads=8, head_dim=128, rank=128, latent_heads=16, experts=16,
-                  identity=4, top=4),
+                  identity=2, top=4),
 }
 
 
@@ -227,12 +227,12 @@ def build_gefovik_pair(size: str, batch: int, context: int):
     hd = z["head_dim"]
     latent = {"type": "latent_attention", "mlp": dense,
               "mixer": dict(heads=z.get("latent_heads", z["heads"]), dim=hd, vdim=hd, kv_rank=z["rank"], scale=hd ** -0.5)}
-    capped = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=30.0,
-                  q_temp={"coef": 0.3, "every": 64})
+    capped = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=50.0,
+                  q_temp={"coef": 0.2, "every": 128})
     four = [latent, {"type": "attention", "mixer": capped, "mlp": routed}, {"type": "attention", "mixer": capped, "mlp": dense},
             {"type": "attention", "mixer": capped, "mlp": routed}]
     gefovik = GefovikConfig(vocab=32768, width=z["width"], layers=tuple(four * (z["layers"] // 4)), norm_eps=1e-6,
-                            embedding_scale=0.5)
+                            embedding_scale=1.0)
     _, qwen, make = build_pair(size, batch, context)
     return gefovik, qwen, make
 

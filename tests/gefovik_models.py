@@ -49,7 +49,7 @@ CONFIGS = {
     "B": {"architecture": "Gefovik", "vocab": 131, "width": 96, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": [
         attention(3, 3, 64, 0.4, dense(50)),
         latent(4, 24, 8, 64, 0.25, moe(4, 1, 5, 36)),
-        attention(2, 1, 96, 0.5, moe(6, 3, 2, 20), softcap=30.0, q_temp=(0.3, 64)),
+        attention(2, 1, 96, 0.5, moe(6, 3, 2, 20), softcap=25.0, q_temp=(0.4, 48)),
         latent(5, 32, 32, 96, 0.2, dense(72))]},
     # C: pages of 32, eight heads on a latent of 128, a bound small enough to flatten most scores, a
     # multiplier that changes every third position

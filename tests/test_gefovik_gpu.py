@@ -358,7 +358,7 @@ def _rows(n, at, device):
                                                                  (16, 2, 2, 1.0, (2.0, 64), 16), (96, 6, 2, 8.0, (0.25, 1), 16),
                                                                  (128, 2, 1, 0.0, (1.0, 16), 16), (24, 3, 3, 5.0, None, 16),
                                                                  (15, 3, 1, 2.0, (0.5, 9), 16), (320, 2, 2, 6.0, None, 16),
-                                                                 (128, 4, 2, 6.0, (0.3, 64), 16), (128, 8, 8, 30.0, None, 32)])
+                                                                 (128, 4, 2, 6.0, (0.35, 48), 16), (128, 8, 8, 20.0, None, 32)])
 def test_capped_attention_with_keys_as_values(cuda_device, dtype, dim, heads, kv_heads, softcap, temp, page):
     """Queries of head 0 point at one key each: a key hundreds of positions back, the first key of the
     sequence, the key just before.  Unit-RMS queries and keys, the multiplier by position, the bound on

@@ -38,8 +38,8 @@ def draw_config(seed: int) -> dict:
         kv_heads = rng.choice([1, 2, 3, 4])
         layers.append(attention(kv_heads * rng.choice([1, 2, 4, 5]), kv_heads, rng.choice([8, 16, 24, 32, 64, 96, 128, 10]),
                                 rng.uniform(0.05, 1.2), feed_forward(),
-                                softcap=rng.choice([None, 0.5, 3.0, 30.0, 50.0]),
-                                q_temp=rng.choice([None, (0.3, 64), (1.5, 1), (0.1, 7), (0.8, 100)])))
+                                softcap=rng.choice([None, 0.5, 3.0, 20.0, 50.0]),
+                                q_temp=rng.choice([None, (0.35, 48), (1.5, 1), (0.1, 7), (0.8, 100)])))
     return {"architecture": "Gefovik", "vocab": rng.randint(50, 300), "width": width,
             "embedding": {"scale": rng.choice([0.25, 0.5, 1.0, 3.0])}, "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
 

@@ -435,7 +435,7 @@ def norms(args) -> dict:
     narrow = (nh + nkv) * hd
     us = _time(lambda i: ops.qkv_pairs(qkv32[i % len(qkv32)][:, :narrow], nh, nkv, hd, hd, None, None, None, 1e-6, None, 0,
                                        positions, token_row, cache, table, status, bf, unit_norm=True, values_from_keys=True,
-                                       q_temp=(0.3, 64)), args.warmup, args.iters)
+                                       q_temp=(0.2, 128)), args.warmup, args.iters)
     moved = T * (narrow * 4 + (nh + 2 * nkv) * hd * 2)
     out["qkv_pairs_keys_as_values"] = {"width": narrow, "us": round(us, 2), "gbs": round(moved / us / 1e3, 1)}
     cos, sin = torch.ones((T, hd // 2), device=device), torch.zeros((T, hd // 2), device=device)
