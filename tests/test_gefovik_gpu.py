@@ -58,7 +58,7 @@ def folders(tmp_path_factory):
 
 @functools.lru_cache(maxsize=256)
 def _plain(folder: str, tokens: tuple):
-    """(logits [T, vocab], the first position whose routing is a close call in either type's sense)."""
+    """(logits [T, vocab], every position's smallest routing margin over the routed layers; inf without any)."""
     config, weights = read_model(folder)
     margins: list = []
     logits = forward(config, weights, list(tokens), margins=margins).numpy()
